@@ -1,0 +1,169 @@
+/* lyap_b200.h -- C ABI of the B200 (sm_100a) Lyapunov-fractal engine.
+ *
+ * One shared library, liblyap_b200.so, plain C types only.  It replaces the compute path of the
+ * reference project (emeraldant/LyapunovFractalWASM); every entry point names the reference
+ * interface it stands in for (paths relative to the reference project).  There is no CPU
+ * fallback: without a CUDA device every compute entry point returns LYAP_ERR_CUDA.
+ *
+ * Conventions
+ *   - every function returns an int status (LYAP_OK == 0); no exception crosses this boundary;
+ *     lyap_last_error() gives the message of the calling thread's last failure.
+ *   - "_device" entry points take DEVICE pointers and only enqueue work on the context's stream;
+ *     the others take HOST pointers, copy, and return when the result is in the host buffer.
+ *   - frames are row-major, row 0 = min_y, column 0 = min_x, like the reference
+ *     (src/lyapunov_fractal.hpp:42,45,84).  Pixel counts are 64-bit here.
+ */
+#ifndef LYAP_B200_H
+#define LYAP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LYAP_ABI_VERSION 1
+
+enum lyap_status {
+    LYAP_OK = 0,
+    LYAP_ERR_INVALID = 1,      /* bad dimension, null pointer, bad row range, unknown mode/palette */
+    LYAP_ERR_SEQUENCE = 2,     /* empty sequence (the reference divides by zero there, :34,37) */
+    LYAP_ERR_TOO_LARGE = 3,    /* step count or size beyond what an entry point supports */
+    LYAP_ERR_CUDA = 4,         /* CUDA runtime failure, or no device */
+    LYAP_ERR_NOMEM = 5,
+    LYAP_ERR_TIMEOUT = 6,      /* a host-side deadline expired (multi-device orchestration) */
+    LYAP_ERR_COMM = 7          /* gather / peer-copy failure */
+};
+
+enum lyap_mode {
+    LYAP_MODE_EXACT = 0,       /* fp64, reference operation order, one log per step: bit-exact */
+    LYAP_MODE_FAST_FP64 = 1,   /* fp64 FMA orbit, product of derivatives, one log per 16 steps */
+    LYAP_MODE_FAST_FP32 = 2    /* fp32 orbit and products, fp64 exponent sum */
+};
+
+enum lyap_palette {            /* web/fractal_renderer.js:207-281; unknown names mean cosmic (:280) */
+    LYAP_PALETTE_COSMIC = 0,
+    LYAP_PALETTE_NEBULA = 1,
+    LYAP_PALETTE_AURORA = 2,
+    LYAP_PALETTE_SOLARFLARE = 3,
+    LYAP_PALETTE_BLACKHOLE = 4,
+    LYAP_PALETTE_PSYCHEDELIC = 5,
+    LYAP_PALETTE_RAINBOW = 6
+};
+
+/* Mirrors lyapunov::FractalComputer::ComputationParams field for field
+ * (src/lyapunov_fractal.hpp:15-25), then an extension block.  lyap_params_default() fills the
+ * reference's defaults (0..4 x 0..4, 800x600, "ABABABAB", 10000 iterations, 100 warm-up). */
+typedef struct lyap_params {
+    double min_x, max_x, min_y, max_y;  /* parameter window: columns -> A, rows -> B */
+    int32_t width, height;
+    const char* sequence;               /* any byte other than 'A' selects B (:37) ... */
+    int32_t sequence_len;
+    int32_t iterations, warmup;
+    /* ---- extension block (all zero = reference behaviour) ---- */
+    int32_t mode;                       /* enum lyap_mode */
+    int32_t palette;                    /* enum lyap_palette */
+    int32_t c_enabled;                  /* ... unless c_enabled: then 'C' selects c_value */
+    int32_t reserved0;
+    double c_value;
+    int64_t row_begin, row_end;         /* rows [row_begin,row_end) of the frame; both 0 = all rows.
+                                           r_y always uses the global row index and global dy, so a
+                                           band has the bits the whole frame would have. */
+} lyap_params;
+
+typedef struct lyap_ctx lyap_ctx;      /* one device, one stream, scratch buffers */
+
+/* Progress callback, same shape as the reference's void(*)(double) (src/lyapunov_fractal.hpp:27).
+ * Called on the calling host thread, in increasing order, after each finished row chunk with
+ * rows_done/height, and once with 1.0 at the end (reference: every 10th row from worker threads
+ * in any order, then 1.0; :88-90,97-99). */
+typedef void (*lyap_progress_fn)(double fraction);
+
+typedef struct lyap_render_stats {
+    uint64_t executed_steps;           /* logistic updates actually performed (early exits excluded) */
+    uint64_t nominal_steps;            /* pixels * (warmup + iterations) */
+    double lambda_min, lambda_max;     /* over finite values > -4 (normalizeData's filter) */
+    float ms_lambda, ms_minmax, ms_normalize, ms_colorize, ms_total_device, ms_copies;
+    int32_t kernel_launches;
+    int32_t reserved;
+} lyap_render_stats;
+
+/* ---- library ---- */
+int lyap_abi_version(void);
+/* Stand-in for testFunction() (src/wasm_bindings.cpp:19-22): returns 42. */
+int lyap_self_test(void);
+const char* lyap_last_error(void);
+const char* lyap_status_string(int status);
+void lyap_params_default(lyap_params* p);
+/* palette id for a name as used by the page's <select> (web/index.html:115-123); unknown -> cosmic */
+int lyap_palette_from_name(const char* name);
+int lyap_device_count(int* count);
+
+/* ---- context ---- */
+int lyap_create(lyap_ctx** ctx, int device);
+int lyap_destroy(lyap_ctx* ctx);
+/* Use a caller-owned cudaStream_t (passed as void*) for all work of this context; NULL = own stream. */
+int lyap_set_stream(lyap_ctx* ctx, void* cuda_stream);
+int lyap_sync(lyap_ctx* ctx);
+int lyap_device_alloc(lyap_ctx* ctx, void** dptr, size_t bytes);
+int lyap_device_free(lyap_ctx* ctx, void* dptr);
+int lyap_host_alloc(void** hptr, size_t bytes);     /* pinned */
+int lyap_host_free(void* hptr);
+int lyap_copy_to_host(lyap_ctx* ctx, void* host, const void* dev, size_t bytes);   /* waits */
+int lyap_copy_to_device(lyap_ctx* ctx, void* dev, const void* host, size_t bytes); /* waits */
+
+/* ---- device-pointer entry points (enqueue only) ---- */
+
+/* FractalComputer::computeFractal (src/lyapunov_fractal.hpp:27-102) for rows [row_begin,row_end).
+ * d_lambda: rows*width doubles, or NULL; d_lambda32: same count of floats ((float)lambda), or NULL.
+ * d_steps: one uint64 the kernel ADDS executed steps to, or NULL. */
+int lyap_lambda_device(lyap_ctx* ctx, const lyap_params* p, double* d_lambda, float* d_lambda32,
+                       uint64_t* d_steps);
+
+/* normalizeData pass 1 (src/lyapunov_fractal.hpp:110-120): d_minmax[0]=min, [1]=max over finite
+ * values > -4; starts from +DBL_MAX / -DBL_MAX like the reference. */
+int lyap_minmax_device(lyap_ctx* ctx, const double* d_values, uint64_t n, double* d_minmax);
+
+/* normalizeData pass 2 (src/lyapunov_fractal.hpp:122-137) with min/max read from device memory
+ * (for a band: the whole frame's min/max).  min >= max gives all zeros (:122). */
+int lyap_normalize_device(lyap_ctx* ctx, const double* d_values, uint64_t n, const double* d_minmax,
+                          double* d_out);
+
+/* applyPostProcessing + palette + ImageData store (web/fractal_renderer.js:283-311,207-281,191-198).
+ * d_norm points at the first of `rows` rows of `width` normalised values; rows_above / rows_below
+ * (0 or 1) say whether the row before / after that block exists in memory (a band's neighbour rows);
+ * where they do not, the image edge rule applies.  d_rgba: rows*width*4 bytes, R,G,B,255. */
+int lyap_colorize_device(lyap_ctx* ctx, const double* d_norm, int32_t width, int64_t rows,
+                         int32_t rows_above, int32_t rows_below, int32_t palette, uint8_t* d_rgba);
+
+/* ---- host-pointer entry points (blocking) ---- */
+
+/* computeFractal (src/lyapunov_fractal.hpp:27): out_lambda holds rows*width doubles. */
+int lyap_compute_fractal(lyap_ctx* ctx, const lyap_params* p, double* out_lambda, lyap_progress_fn progress);
+
+/* normalizeData (src/lyapunov_fractal.hpp:105): n == 0 is allowed and does nothing (:106). */
+int lyap_normalize_data(lyap_ctx* ctx, const double* values, uint64_t n, double* out);
+
+/* renderFractal up to putImageData (web/fractal_renderer.js:177-200) for a whole frame. */
+int lyap_colorize(lyap_ctx* ctx, const double* norm, int32_t width, int32_t height, int32_t palette,
+                  uint8_t* out_rgba);
+
+/* The binding's whole call order (src/wasm_bindings.cpp:109-125: parse, computeFractal,
+ * normalizeData) followed by the page's colour stage, on the whole frame.  Any output may be NULL.
+ * out_norm is what the WASM export returns. */
+int lyap_render(lyap_ctx* ctx, const lyap_params* p, double* out_lambda, float* out_lambda32, double* out_norm,
+                uint8_t* out_rgba, lyap_progress_fn progress, lyap_render_stats* stats);
+
+/* ---- measurement ---- */
+
+/* Issue-rate micro-benchmark of the fp64 pipe on the context's device: independent DFMA chains,
+ * all SMs.  Writes thread-level fp64 instructions per second. */
+int lyap_fp64_peak(lyap_ctx* ctx, double* instr_per_second);
+/* Same for the fp32 FMA pipe. */
+int lyap_fp32_peak(lyap_ctx* ctx, double* instr_per_second);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LYAP_B200_H */

@@ -1,0 +1,281 @@
+// lyap_kernels_fast.cuh -- fast-mode lambda kernels (included by lyap_kernels.cu).
+//
+// Same pixel mapping, sequence handling, sentinel and early-exit rules as the exact kernel, but the
+// arithmetic is rearranged for speed and is NOT bit-compatible with the reference:
+//   t = r*x;  deriv = fma(-2,t,r) = r(1-2x);  x' = fma(-t,x,t) = r x (1-x)         (4 fused ops/step)
+// and instead of one log per step the |deriv| are multiplied together; the product's exponent is
+// moved into an integer every 16 (fp64) or 4 (fp32) steps, and one log of the remaining mantissa is
+// taken per pixel at the end:  sum log|deriv| = E*ln2 + log(mantissa product).
+// A chunk in which the orbit left (0,1) or a derivative was exactly zero is rolled back and redone
+// step by step with the reference's rules (skip zero terms, stop at the exit, keep the partial sum).
+#pragma once
+
+namespace lyap {
+
+template <typename T>
+struct FastTraits;
+
+template <>
+struct FastTraits<double> {
+    static constexpr int kRenorm = 16;
+    static __device__ __forceinline__ double fma_(double a, double b, double c) { return __fma_rn(a, b, c); }
+    static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
+    static __device__ __forceinline__ double abs_(double a) { return fabs(a); }
+    // returns biased exponent; rewrites v's exponent to 0 (mantissa in [1,2)); sign assumed +
+    static __device__ __forceinline__ int strip(double& v) {
+        const unsigned hw = (unsigned)__double2hiint(v);
+        v = __hiloint2double((int)((hw & 0x000FFFFFu) | 0x3FF00000u), __double2loint(v));
+        return (int)(hw >> 20);
+    }
+    static constexpr int kBias = 1023;
+    static constexpr int kExpMax = 2047;
+};
+
+template <>
+struct FastTraits<float> {
+    static constexpr int kRenorm = 4;
+    static __device__ __forceinline__ float fma_(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+    static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+    static __device__ __forceinline__ float abs_(float a) { return fabsf(a); }
+    static __device__ __forceinline__ int strip(float& v) {
+        const unsigned u = __float_as_uint(v);
+        v = __uint_as_float((u & 0x007FFFFFu) | 0x3F800000u);
+        return (int)(u >> 23);
+    }
+    static constexpr int kBias = 127;
+    static constexpr int kExpMax = 255;
+};
+
+template <typename T>
+struct FastPixel {
+    T x;
+    double extra;   // log terms added one by one by the careful path
+    int valid;
+};
+
+template <typename T, bool ACC>
+__device__ __noinline__ bool fast_careful_chunk(FastPixel<T>* ps, T rA, T rB, T rC, unsigned word, int n,
+                                                unsigned long long* steps) {
+    using F = FastTraits<T>;
+    T x = ps->x;
+    double extra = ps->extra;
+    int valid = ps->valid;
+    bool dead = false;
+    int j = 0;
+    for (; j < n; ++j) {
+        const unsigned sel = (word >> (2 * j)) & 3u;
+        const T r = sel == 0 ? rA : (sel == 1 ? rB : rC);
+        const T t = F::mul(r, x);
+        if (ACC) {
+            const T d = F::abs_(F::fma_((T)-2, t, r));
+            if (d > (T)0) {
+                extra = __dadd_rn(extra, lyap_log_tab((double)d, g_lyap_logtab, 1));
+                ++valid;
+            }
+        }
+        x = F::fma_(-t, x, t);
+        if (!(x > (T)0 && x < (T)1)) {
+            dead = true;
+            ++j;
+            break;
+        }
+    }
+    *steps += (unsigned long long)j;
+    ps->x = x;
+    ps->extra = extra;
+    ps->valid = valid;
+    return dead;
+}
+
+template <typename T, int P, bool ACC>
+__device__ __forceinline__ void fast_mode_steps(T (&x)[P], T (&prod)[P], const T (&r)[P]) {
+    using F = FastTraits<T>;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+        const T t = F::mul(r[p], x[p]);
+        if (ACC) prod[p] = F::mul(prod[p], F::abs_(F::fma_((T)-2, t, r[p])));
+        x[p] = F::fma_(-t, x[p], t);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ bool ordinary_param_t(T r);
+template <>
+__device__ __forceinline__ bool ordinary_param_t<double>(double r) { return r > 0x1p-40 && r < 0x1p40; }
+template <>
+__device__ __forceinline__ bool ordinary_param_t<float>(float r) { return r > 0x1p-20f && r < 0x1p5f; }
+
+template <typename T, int P, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,
+              unsigned long long* __restrict__ steps_out) {
+    using F = FastTraits<T>;
+    unsigned long long my_steps = 0;
+    const long long tile_px = (long long)THREADS * P;
+
+    for (long long tile = blockIdx.x; tile * tile_px < a.n_pixels; tile += gridDim.x) {
+        const long long idx0 = tile * tile_px + (long long)threadIdx.x * P;
+        T x[P], prod[P], rA[P], rB[P], rC[P];
+        double extra[P];
+        int valid[P], esum[P];
+        bool done[P], careful_only[P];
+        {
+            long long row = idx0 / a.width;
+            int col = (int)(idx0 - row * a.width);
+            row += a.row_begin;
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                const bool inside = idx0 + p < a.n_pixels;
+                const double rb = __dadd_rn(a.min_y, __dmul_rn(a.dy, (double)(int)row));
+                const double ra = __dadd_rn(a.min_x, __dmul_rn(a.dx, (double)col));
+                rA[p] = (T)ra;
+                rB[p] = (T)rb;
+                rC[p] = (T)a.c_value;
+                x[p] = (T)0.5;
+                prod[p] = (T)1;
+                extra[p] = 0.0;
+                valid[p] = 0;
+                esum[p] = 0;
+                done[p] = !inside || ra <= 0.0 || rb <= 0.0;
+                careful_only[p] = !(ordinary_param_t<T>(rA[p]) && ordinary_param_t<T>(rB[p]) && a.fast_ok_c);
+                if (++col == a.width) {
+                    col = 0;
+                    ++row;
+                }
+            }
+        }
+
+        for (int region = 0; region < 2; ++region) {
+            const bool acc = region == 1;
+            const int nsteps = acc ? a.iterations : a.warmup;
+            const int word0 = acc ? a.acc_word0 : 0;
+            const int nchunks = (nsteps + kStepsPerWord - 1) / kStepsPerWord;
+            for (int c = 0; c < nchunks; ++c) {
+                bool all_done = true;
+#pragma unroll
+                for (int p = 0; p < P; ++p) all_done = all_done && done[p];
+                if (__all_sync(0xFFFFFFFFu, all_done)) break;
+
+                const unsigned word = a.sel[word0 + c];
+                const int n = min(kStepsPerWord, nsteps - c * kStepsPerWord);
+                T sx[P], sp[P];
+                int se[P], emin[P], emax[P];
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    sx[p] = x[p];
+                    sp[p] = prod[p];
+                    se[p] = esum[p];
+                    emin[p] = F::kExpMax;
+                    emax[p] = 0;
+                }
+                unsigned w = word;
+                if (acc) {
+                    for (int j0 = 0; j0 < n; j0 += F::kRenorm) {
+                        const int jn = min(F::kRenorm, n - j0);
+                        for (int j = 0; j < jn; ++j, w >>= 2) {
+                            const unsigned sel = w & 3u;
+                            if (sel == 0) fast_mode_steps<T, P, true>(x, prod, rA);
+                            else if (sel == 1) fast_mode_steps<T, P, true>(x, prod, rB);
+                            else fast_mode_steps<T, P, true>(x, prod, rC);
+                        }
+#pragma unroll
+                        for (int p = 0; p < P; ++p) {
+                            const int e = F::strip(prod[p]);
+                            emin[p] = min(emin[p], e);
+                            emax[p] = max(emax[p], e);
+                            esum[p] += e - F::kBias;
+                        }
+                    }
+                } else {
+                    for (int j = 0; j < n; ++j, w >>= 2) {
+                        const unsigned sel = w & 3u;
+                        if (sel == 0) fast_mode_steps<T, P, false>(x, prod, rA);
+                        else if (sel == 1) fast_mode_steps<T, P, false>(x, prod, rB);
+                        else fast_mode_steps<T, P, false>(x, prod, rC);
+                    }
+                }
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    if (done[p]) continue;
+                    // a zero derivative or an overflow shows as exponent field 0 / all ones
+                    const bool regular = !careful_only[p] && (x[p] > (T)0 && x[p] < (T)1) &&
+                                         (!acc || (emin[p] != 0 && emax[p] != F::kExpMax));
+                    if (regular) {
+                        if (acc) valid[p] += n;
+                        my_steps += (unsigned long long)n;
+                    } else {
+                        esum[p] = se[p];
+                        prod[p] = sp[p];
+                        FastPixel<T> ps{sx[p], extra[p], valid[p]};
+                        const bool dead =
+                            acc ? fast_careful_chunk<T, true>(&ps, rA[p], rB[p], rC[p], word, n, &my_steps)
+                                : fast_careful_chunk<T, false>(&ps, rA[p], rB[p], rC[p], word, n, &my_steps);
+                        x[p] = ps.x;
+                        extra[p] = ps.extra;
+                        valid[p] = ps.valid;
+                        if (dead) {
+                            done[p] = true;
+                            x[p] = (T)0.25;
+                        }
+                    }
+                }
+            }
+        }
+
+        double lam[P];
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+            // sum of logs = esum*ln2 + log(mantissa product) + terms logged one by one
+            const double lsum = __dadd_rn(
+                __fma_rn((double)esum[p], LYAP_LN2, lyap_log_tab((double)prod[p], g_lyap_logtab, 1)), extra[p]);
+            lam[p] = valid[p] > 0 ? __ddiv_rn(lsum, __dmul_rn((double)valid[p], LYAP_LN2)) : -5.0;
+        }
+        if (out64) {
+#pragma unroll
+            for (int p = 0; p < P; ++p)
+                if (idx0 + p < a.n_pixels) out64[idx0 + p] = lam[p];
+        }
+        if (out32) {
+#pragma unroll
+            for (int p = 0; p < P; ++p)
+                if (idx0 + p < a.n_pixels) out32[idx0 + p] = (float)lam[p];
+        }
+    }
+
+    if (steps_out) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) my_steps += __shfl_down_sync(0xFFFFFFFFu, my_steps, o);
+        if ((threadIdx.x & 31) == 0 && my_steps) atomicAdd(steps_out, my_steps);
+    }
+}
+
+constexpr int kFastThreads = 256;
+
+template <typename T, int P>
+static cudaError_t launch_lambda_fast_t(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                        int sm_count, cudaStream_t st) {
+    const long long tile_px = (long long)kFastThreads * P;
+    const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
+    if (tiles <= 0) return cudaSuccess;
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_lambda_fast<T, P, kFastThreads>,
+                                                                  kFastThreads, 0);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) per_sm = 1;
+    const long long cap = (long long)sm_count * per_sm;
+    const int grid = (int)(tiles < cap ? tiles : cap);
+    k_lambda_fast<T, P, kFastThreads><<<grid, kFastThreads, 0, st>>>(a, out64, out32, steps);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                 int sm_count, cudaStream_t st) {
+    return launch_lambda_fast_t<double, 4>(a, out64, out32, steps, sm_count, st);
+}
+
+cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                 int sm_count, cudaStream_t st) {
+    return launch_lambda_fast_t<float, 4>(a, out64, out32, steps, sm_count, st);
+}
+
+}  // namespace lyap
