@@ -116,9 +116,14 @@ k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, 
     for (long long tile = blockIdx.x; tile * tile_px < a.n_pixels; tile += gridDim.x) {
         const long long idx0 = tile * tile_px + (long long)threadIdx.x * P;
         T x[P], prod[P], rA[P], rB[P], rC[P];
-        double extra[P];
+        double extra[P], lam[P];
         int valid[P], esum[P];
         bool done[P], careful_only[P];
+        // lambda from the three partial sums: esum*ln2 + log(mantissa product) + terms logged one by one
+        auto finish = [&](int e, T m, double ex, int nvalid) -> double {
+            const double lsum = __dadd_rn(__fma_rn((double)e, LYAP_LN2, lyap_log_tab((double)m, g_lyap_logtab, 1)), ex);
+            return nvalid > 0 ? __ddiv_rn(lsum, __dmul_rn((double)nvalid, LYAP_LN2)) : -5.0;
+        };
         {
             long long row = idx0 / a.width;
             int col = (int)(idx0 - row * a.width);
@@ -136,6 +141,7 @@ k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, 
                 extra[p] = 0.0;
                 valid[p] = 0;
                 esum[p] = 0;
+                lam[p] = -5.0;
                 done[p] = !inside || ra <= 0.0 || rb <= 0.0;
                 careful_only[p] = !(ordinary_param_t<T>(rA[p]) && ordinary_param_t<T>(rB[p]) && a.fast_ok_c);
                 if (++col == a.width) {
@@ -214,7 +220,9 @@ k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, 
                         extra[p] = ps.extra;
                         valid[p] = ps.valid;
                         if (dead) {
+                            // freeze the result now: the abandoned lane keeps running on garbage
                             done[p] = true;
+                            lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
                             x[p] = (T)0.25;
                         }
                     }
@@ -222,14 +230,9 @@ k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, 
             }
         }
 
-        double lam[P];
 #pragma unroll
-        for (int p = 0; p < P; ++p) {
-            // sum of logs = esum*ln2 + log(mantissa product) + terms logged one by one
-            const double lsum = __dadd_rn(
-                __fma_rn((double)esum[p], LYAP_LN2, lyap_log_tab((double)prod[p], g_lyap_logtab, 1)), extra[p]);
-            lam[p] = valid[p] > 0 ? __ddiv_rn(lsum, __dmul_rn((double)valid[p], LYAP_LN2)) : -5.0;
-        }
+        for (int p = 0; p < P; ++p)
+            if (!done[p]) lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
         if (out64) {
 #pragma unroll
             for (int p = 0; p < P; ++p)

@@ -1,0 +1,128 @@
+"""GPU tests of the C ABI's behaviour around the kernels: host entry points, device entry points per
+band, error statuses, the progress callback, fast modes within their stated tolerance."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import lyapunovfractalwasm_b200 as L
+from lyapunovfractalwasm_b200 import bands
+from conftest import CONFIGS
+
+pytestmark = pytest.mark.gpu
+
+
+def test_normalize_data_entry_point(engine, port):
+    rng = np.random.default_rng(3)
+    v = rng.uniform(-6, 1.5, size=100003)
+    v[::97] = -5.0
+    v[5] = np.nan
+    v[6] = np.inf
+    v[7] = -np.inf
+    got = engine.normalize_data(v)
+    assert np.array_equal(got.view(np.uint64), port.normalize(v).view(np.uint64))
+    assert np.all(engine.normalize_data(np.full(1000, 0.3)) == 0.0)       # min >= max (:122)
+    assert np.all(engine.normalize_data(np.full(7, -5.0)) == 0.0)         # nothing passes the filter
+    assert engine.normalize_data(np.empty(0)).size == 0                   # empty in, empty out (:106)
+    one = engine.normalize_data(np.array([0.5]))
+    assert one[0] == 0.0
+
+
+def test_colorize_entry_point_all_palettes(engine, port):
+    rng = np.random.default_rng(4)
+    norm = rng.uniform(0, 1, size=(37, 53))
+    norm[0, 0] = 0.0
+    norm[1, 1] = 1.0
+    norm[2, 2] = 0.5
+    for pal in range(7):
+        assert np.array_equal(engine.colorize(norm, pal), port.colorize(norm, pal)), pal
+    assert np.array_equal(engine.colorize(norm, 42), port.colorize(norm, 0))
+
+
+def test_device_entry_points_band_by_band(engine, port):
+    """Three bands with recomputed halo rows and an exchanged min/max give the single-frame bytes."""
+    kw = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=300, height=101, sequence="AABAB", iterations=150,
+              warmup=30)
+    whole = engine.render(L.make_params(**kw), want=("lambda", "norm", "rgba"))
+    backend = bands.GpuBackend(engine, L.make_params)
+    world = 3
+    local = []
+    for rank in range(world):
+        b, e = bands.band_rows(kw["height"], world, rank)
+        h = backend.lambda_rows(kw, b, e)
+        local.append(backend.minmax(h))
+    glo, ghi = min(m[0] for m in local), max(m[1] for m in local)
+    parts = [bands.render_band(backend, kw, rank, world, lambda lo, hi: (glo, ghi)) for rank in range(world)]
+    lam = np.vstack([backend.to_host(p["lambda"]) for p in parts])
+    norm = np.vstack([backend.to_host(p["norm"]) for p in parts])
+    rgba = np.vstack([backend.to_host(p["rgba"]) for p in parts])
+    assert np.array_equal(lam.view(np.uint64), whole["lambda"].view(np.uint64))
+    assert np.array_equal(norm.view(np.uint64), whole["norm"].view(np.uint64))
+    assert np.array_equal(rgba, whole["rgba"])
+
+
+def test_error_statuses(engine):
+    lib = engine.lib
+    out = np.empty(64)
+
+    def status(**kw):
+        p = L.make_params(**dict(dict(width=8, height=8, sequence="AB", iterations=10, warmup=2), **kw))
+        return lib.lyap_compute_fractal(engine.ctx, ctypes.byref(p), out.ctypes.data, None)
+
+    assert status() == 0
+    assert status(sequence="") == 2 and b"empty" in lib.lyap_last_error()
+    assert status(width=0) == 1 and status(height=-3) == 1
+    assert status(iterations=-1) == 1 and status(warmup=-1) == 1
+    assert status(mode=7) == 1
+    assert status(row_begin=5, row_end=3) == 1 and status(row_begin=0, row_end=9) == 1
+    assert status(iterations=20000) == 3
+    p = L.make_params(width=8, height=8, sequence="AB", iterations=10, warmup=2)
+    assert lib.lyap_compute_fractal(engine.ctx, ctypes.byref(p), None, None) == 1
+    assert lib.lyap_compute_fractal(None, ctypes.byref(p), out.ctypes.data, None) == 1
+    # a band cannot be normalised by the host entry point (needs the frame's min/max)
+    pb = L.make_params(width=8, height=8, sequence="AB", iterations=10, warmup=2, row_begin=2, row_end=4)
+    assert lib.lyap_render(engine.ctx, ctypes.byref(pb), None, None, out.ctypes.data, None, None, None) == 1
+    bad = ctypes.c_void_p()
+    assert lib.lyap_create(ctypes.byref(bad), 9999) == 1
+
+
+def test_progress_callback_is_ordered_and_ends_with_one(engine, port):
+    kw = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=2048, height=2048, sequence="AB", iterations=60,
+              warmup=10)
+    seen = []
+    lam = engine.compute_fractal(L.make_params(**kw), progress=seen.append)
+    assert len(seen) >= 2 and seen[-1] == 1.0
+    assert all(0.0 < a < b <= 1.0 for a, b in zip(seen, seen[1:]))
+    # chunked launches do not change the result
+    again = engine.compute_fractal(L.make_params(**kw))
+    assert np.array_equal(lam.view(np.uint64), again.view(np.uint64))
+
+
+def test_fast_modes_within_stated_tolerance(engine):
+    """Fast modes against exact on the config-1 frame.  Stated bounds: fp64 fast mode keeps 99% of the
+    stable pixels (lambda < 0, > -4) within 1e-6 relative; fp32 fast mode keeps their median within 1e-5
+    relative.  Chaotic pixels (lambda >= 0) agree only statistically: mean lambda over them within 2e-3 (fp64) and
+    1e-2 (fp32, whose 24-bit orbits fall into short cycles sooner)."""
+    kw = CONFIGS[1]
+    exact = engine.render(L.make_params(**kw), want=("lambda",))["lambda"]
+    stable = (exact < 0) & (exact > -4)
+    chaotic = exact >= 0
+    for mode, frac_bound, median_bound, mean_bound in ((L.MODE_FAST_FP64, 0.01, 1e-12, 2e-3),
+                                                        (L.MODE_FAST_FP32, 1.0, 1e-5, 1e-2)):
+        fast = engine.render(L.make_params(**kw, mode=mode), want=("lambda", "rgba"))
+        lam = fast["lambda"]
+        # same sentinel pixels, except on the last row / column where a parameter is exactly 4: there
+        # the full-range map can land on x == 1.0 at a different step in rearranged arithmetic
+        differs = (lam == -5.0) != (exact == -5.0)
+        assert not differs[:-1, :-1].any()
+        rel = np.abs(lam[stable] - exact[stable]) / np.abs(exact[stable])
+        assert np.mean(rel > 1e-6) <= frac_bound, (mode, np.mean(rel > 1e-6))
+        assert np.median(rel) < median_bound, (mode, np.median(rel))
+        bias = abs(np.mean(lam[chaotic]) - np.mean(exact[chaotic]))
+        assert bias < mean_bound, (mode, bias)
+        assert fast["rgba"].shape == (512, 512, 4) and np.all(fast["rgba"][..., 3] == 255)
+
+
+def test_peak_microbenchmarks_report_plausible_rates(engine):
+    f64, f32 = engine.fp64_peak(), engine.fp32_peak()
+    assert 5e12 < f64 < 3e13 and 1e13 < f32 < 6e13

@@ -1,0 +1,136 @@
+"""Pins the CPU restatement (oracle/oracle_port.cpp) to the reference.
+
+1. against the committed golden vectors, which were produced by the UNMODIFIED reference header
+   (tests/golden/make_golden.py) -- runs everywhere;
+2. directly against oracle/_ref (the same header compiled here) when it is present;
+3. hand-checkable known answers and the reference's quirks (reference src/lyapunov_fractal.hpp)."""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+
+
+def run_port(port, args, **kw):
+    lam, steps = port.lambda_rows(*args, **kw)
+    return lam, steps
+
+
+def test_port_matches_golden_vectors(port, golden):
+    for name, case in golden["cases"].items():
+        args = case["args"]
+        lam, _ = run_port(port, args)
+        norm = port.normalize(lam)
+        g = case["lyapmath"]
+        assert "%016x" % port.hash64(lam) == g["lambda_hash"], name
+        assert "%016x" % port.hash64(norm) == g["norm_hash"], name
+        for x, y, lh, nh in case["spots"]:
+            assert lam[y, x] == float.fromhex(lh) and norm[y, x] == float.fromhex(nh), (name, x, y)
+        for pname, h in case.get("rgba_hash", {}).items():
+            assert "%016x" % port.hash64(port.colorize(norm, O.PALETTES.index(pname))) == h, (name, pname)
+
+
+def test_port_matches_reference_header_built_here(port, golden):
+    ref = O.ref("lyapmath")
+    if ref is None:
+        pytest.skip("oracle/_ref not present (reference sources absent): covered by the golden vectors")
+    for name, case in golden["cases"].items():
+        args = case["args"]
+        a = ref.compute_fractal(*args)
+        b, _ = run_port(port, args)
+        assert np.array_equal(a.view(np.uint64), b.view(np.uint64)), name
+        assert np.array_equal(ref.normalize(a).view(np.uint64), port.normalize(b).view(np.uint64)), name
+    f4, i4, seq = ref.default_params()
+    assert f4 == [0.0, 4.0, 0.0, 4.0] and i4 == [800, 600, 10000, 100] and seq == "ABABABAB"
+
+
+def test_stock_libm_build_is_last_bit_close(port, golden):
+    """The header linked to the host libm ("the natively compiled reference") against the header
+    linked to this project's math: same sentinels, lambda within 1e-12 relative (or 1e-13 absolute
+    next to zero), identical RGBA bytes.  Known hashes of two glibc variants are recognised."""
+    stock, mine = O.ref("stock"), O.ref("lyapmath")
+    if stock is None:
+        pytest.skip("oracle/_ref not present")
+    args = golden["cases"]["cfg1_512_AB"]["args"]
+    a, b = stock.compute_fractal(*args), mine.compute_fractal(*args)
+    assert np.array_equal(a == -5.0, b == -5.0)
+    assert np.all(np.abs(a - b) <= np.maximum(1e-12 * np.abs(b), 1e-13))
+    na, nb = stock.normalize(a), mine.normalize(b)
+    assert np.max(np.abs(na - nb)) < 1e-12
+    assert np.array_equal(port.colorize(na), port.colorize(nb))
+    h = "%016x" % port.hash64(a)
+    if h not in ("9620151bc493006b", "ce2e780709b86f86"):
+        pytest.skip("host libm variant not one of the two recorded ones (lambda hash %s)" % h)
+
+
+def test_known_answers(port):
+    # (a,b) = (2,2), "AB": x stays at 0.5, derivative 0 every step -> no valid term -> -5 (:71-74,84-85)
+    lam, steps = port.lambda_rows(2.0, 4.0, 2.0, 4.0, 3, 3, "AB", 50, 10)
+    assert lam[0, 0] == -5.0
+    # a = 4 column: first step gives x = 1.0 -> break in warm-up -> -5 (:60-62,65)
+    assert np.all(lam[:, 2] == -5.0)
+    # r <= 0 -> -5 without iterating (:47-50)
+    lam, steps = port.lambda_rows(-1.0, 0.0, 2.0, 3.0, 4, 2, "AB", 50, 10)
+    assert np.all(lam == -5.0) and steps == 0
+    # width 1: dx = inf, r_x = NaN -> -5 (:29,45)
+    lam, _ = port.lambda_rows(2.0, 4.0, 2.0, 4.0, 1, 4, "AB", 50, 10)
+    assert np.all(lam == -5.0)
+    # all values equal -> min >= max -> zeros (:122); empty filter set too
+    assert np.all(port.normalize(np.full(10, 0.25)) == 0.0)
+    assert np.all(port.normalize(np.full(10, -5.0)) == 0.0)
+    # a stable fixed point: r = 2.5 everywhere, x* = 0.6, lambda = log2|2.5*(1-1.2)| = -1
+    lam, _ = port.lambda_rows(2.5, 2.6, 2.5, 2.6, 2, 2, "AB", 4000, 1000)
+    assert abs(lam[0, 0] + 1.0) < 1e-12
+
+
+def test_sequence_rules(port):
+    base = (2.6, 3.9, 2.7, 3.8, 24, 16)
+    a, _ = port.lambda_rows(*base, "AbaB", 200, 20)
+    b, _ = port.lambda_rows(*base, "ABBB", 200, 20)
+    assert np.array_equal(a.view(np.uint64), b.view(np.uint64))          # any non-'A' byte is B (:37)
+    a, _ = port.lambda_rows(*base, "ABC", 200, 20)
+    b, _ = port.lambda_rows(*base, "ABB", 200, 20)
+    assert np.array_equal(a.view(np.uint64), b.view(np.uint64))          # 'C' is B while the extension is off
+    c, _ = port.lambda_rows(*base, "ABC", 200, 20, c=3.7)
+    assert not np.array_equal(b, c)
+    # phase runs on through warm-up (:56,66): warm-up 3 of "AB" makes accumulation start on 'B'
+    a, _ = port.lambda_rows(*base, "AB", 100, 3)
+    b, _ = port.lambda_rows(*base, "AB", 100, 4)
+    assert not np.array_equal(a, b)
+
+
+def test_transpose_symmetry(port):
+    # swapping the two parameter ranges and complementing the sequence transposes the image
+    a, _ = port.lambda_rows(2.5, 4.0, 3.0, 3.9, 48, 48, "AAB", 300, 50)
+    b, _ = port.lambda_rows(3.0, 3.9, 2.5, 4.0, 48, 48, "BBA", 300, 50)
+    assert np.array_equal(a.view(np.uint64), b.T.copy().view(np.uint64))
+
+
+def test_band_and_stride_invariance(port):
+    args = (2.5, 4.0, 2.5, 4.0, 64, 50, "AABAB", 150, 20)
+    whole, steps = port.lambda_rows(*args)
+    parts, psteps = [], 0
+    for y0, y1 in ((0, 7), (7, 8), (8, 33), (33, 50)):
+        p, s = port.lambda_rows(*args, y0=y0, y1=y1)
+        parts.append(p)
+        psteps += s
+    assert np.array_equal(np.vstack(parts).view(np.uint64), whole.view(np.uint64)) and psteps == steps
+    strided, _ = port.lambda_rows(*args, y0=3, y1=50, row_stride=7)
+    assert np.array_equal(strided.view(np.uint64), whole[3:50:7].view(np.uint64))
+
+
+def test_palette_known_values(port):
+    assert port.palette(0.5, 0) == (204, 76, 255)          # cosmic at the centre: I = 1, phase = 0
+    assert port.palette(0.0, 0) == (0, 0, 0)               # floor(255*(0.1*cos(pi))) = -26 -> clamped to 0
+    assert port.palette(1.0, 0) == (0, 0, 0)
+    assert port.palette(0.5, 3) == (242, 153, 51)          # solarflare: floor(255*.95), floor(255*.6), floor(255*.2)
+    assert port.palette(0.5, 6) == (0, 254, 255)           # rainbow, hue 180: (2/3 - 1/2)*6 rounds just below 1
+    assert port.palette(0.5, 99) == port.palette(0.5, 0)   # unknown -> cosmic (web/fractal_renderer.js:280)
+    assert port.palette(float("nan"), 0) == (0, 0, 0)
+
+
+def test_box_mean_counts(port):
+    v = np.arange(12, dtype=np.float64).reshape(3, 4)
+    b = port.box3(v)
+    assert b[0, 0] == (0 + 1 + 4 + 5) / 4 and b[1, 1] == np.sum(v[0:3, 0:3]) / 9 and b[0, 1] == (1 + 0 + 2 + 4 + 5 + 6) / 6
+    one = port.box3(np.array([[0.75]]))
+    assert one[0, 0] == 0.75
