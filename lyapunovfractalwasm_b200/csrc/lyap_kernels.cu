@@ -8,6 +8,7 @@
 // Build with -fmad=false: the exact kernels may only fuse where an fma is written out.
 #include <cfloat>
 #include <cstdint>
+#include <cstdlib>
 
 #include "lyap_engine.h"
 #include "lyap_math.h"
@@ -21,7 +22,9 @@ __device__ const lyap_logtab_entry g_lyap_logtab[LYAP_LOG_BINS] = {LYAP_LOG_TABL
 //
 // One thread owns P horizontally adjacent pixels for their whole orbit: x, the running log sum and
 // the two parameter values stay in registers.  The per-step A/B(/C) choice is the same for every
-// pixel, so it is a warp-uniform branch on two bits of a kernel-parameter word.
+// pixel, so steps are taken in groups of U whose pattern (e.g. "AB", "BA") picks, by one warp-uniform
+// multiway branch, a straight-line body compiled for exactly that pattern: no per-step select or branch.
+// Inside a body the orbit runs ahead and the U*P logarithms that hang off it are independent chains.
 //
 // The log table (1024 entries x 16 B) sits in shared memory in 8 interleaved copies: entry i of
 // copy c is at slot i*8+c and a lane uses copy (lane & 7).  A 16-byte load per lane is served per
@@ -32,7 +35,7 @@ __device__ const lyap_logtab_entry g_lyap_logtab[LYAP_LOG_BINS] = {LYAP_LOG_TABL
 // is permanent for x <- r x (1-x) with r > 0 (x >= 1 gives x <= 0 next, x <= 0 stays <= 0, NaN stays
 // NaN), so testing x after the chunk finds every exit, and the only other irregular event, a zero
 // derivative (x == 0.5 exactly, skipped and not counted by the reference, :71-74), shows up as a
-// zero exponent field, tracked with one integer min per step.  A chunk in which anything irregular
+// zero exponent field, tracked with an integer min over the steps.  A chunk in which anything irregular
 // happened is rolled back and redone by `careful_chunk`, which follows the reference step by step.
 // ---------------------------------------------------------------------------------------------
 
@@ -56,7 +59,7 @@ struct PixelState {
 // Returns true when the orbit left (0,1) (the reference's break).  *steps counts executed updates.
 template <bool ACC>
 __device__ __noinline__ bool careful_chunk(PixelState* ps, double rA, double rB, double rC, unsigned word, int n,
-                                           const lyap_logtab_entry* tab, unsigned long long* steps) {
+                                           unsigned long long* steps) {
     double x = ps->x, lyap = ps->lyap;
     int valid = ps->valid;
     bool dead = false;
@@ -67,7 +70,7 @@ __device__ __noinline__ bool careful_chunk(PixelState* ps, double rA, double rB,
         if (ACC) {
             const double deriv = fabs(__dmul_rn(r, __dsub_rn(1.0, __dmul_rn(2.0, x))));   // :69
             if (deriv > 0.0) {                                                              // :71
-                lyap = __dadd_rn(lyap, lyap_log_tab(deriv, tab, kTabCopies));               // :72
+                lyap = __dadd_rn(lyap, lyap_log_tab(deriv, g_lyap_logtab, 1));              // :72
                 ++valid;
             }
         }
@@ -85,33 +88,196 @@ __device__ __noinline__ bool careful_chunk(PixelState* ps, double rA, double rB,
     return dead;
 }
 
-template <int P, bool ACC>
-__device__ __forceinline__ void fast_steps(double (&x)[P], double (&lyap)[P], int (&kemin)[P], const double (&r)[P],
-                                           const lyap_logtab_entry* tab) {
+// Constants of the log core in constant memory: fp64 instructions take them as constant-bank
+// operands, which costs no instruction (64-bit immediates would each need two moves).
+struct LogConsts {
+    double c2, c3, c4, ln2hi, ln2lo, klo_bias;
+};
+__constant__ LogConsts c_logk = {LYAP_LOG_C2, LYAP_LOG_C3, LYAP_LOG_C4, LYAP_LN2HI, LYAP_LN2LO, LYAP_KLO_BIAS};
+
+// lyap_log_core (lyap_math.h) for a positive normal d, written against the interleaved shared-memory
+// table: `tab_addr` is the shared-window byte address of this lane's copy of entry 0, entries are
+// kTabCopies*16 bytes apart.  Same operations in the same order as lyap_log_core, so same bits.
+__device__ __forceinline__ double log_fast(double d, unsigned tab_addr, unsigned& hw_out) {
+    const unsigned hw = (unsigned)__double2hiint(d);
+    hw_out = hw;
+    const unsigned off = (hw >> 3) & (unsigned)((LYAP_LOG_BINS - 1) * kTabCopies * 16);   // bin index * 128 bytes
+    double lp, invcb;
+    asm("ld.shared.v2.f64 {%0, %1}, [%2];" : "=d"(lp), "=d"(invcb) : "r"(tab_addr + off));
+    // The shared copy holds invc with 0x3FF00000 added to its high word, so subtracting d's exponent field
+    // gives invc * 2^-(exponent of d): d * that == mantissa(d) * invc exactly (a power-of-two rescaling),
+    // without assembling the mantissa as a separate double.
+    const double invs = __hiloint2double(__double2hiint(invcb) - (int)(hw & 0xFFF00000u), __double2loint(invcb));
+    const double kd = (double)(int)(hw >> 20);
+    const double r = __fma_rn(d, invs, -1.0);
+    double q = __fma_rn(r, c_logk.c4, c_logk.c3);
+    q = __fma_rn(r, q, c_logk.c2);
+    const double w = __fma_rn(r, q, 1.0);
+    const double klo = __fma_rn(kd, c_logk.ln2lo, c_logk.klo_bias);
+    const double s = __fma_rn(r, w, klo);
+    const double hi = __fma_rn(kd, c_logk.ln2hi, lp);
+    return __dadd_rn(hi, s);
+}
+
+// U consecutive logistic steps of all P pixels, selector bits in `word` (step j at bits 2j, 2j+1).
+// Written as one straight-line block: the orbit x (3 dependent fp64 operations per step) runs ahead
+// and leaves the U derivatives behind, whose logarithms are independent of each other and of the orbit,
+// so the scheduler has U*P log chains to interleave.  The sum is still accumulated in step order.
+// The warp-uniform parameter choice is a select (no branch, so the block stays one scheduling region).
+template <int P, bool ACC, bool HAS_C, int U>
+__device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P], const double (&rA)[P],
+                                           const double (&rB)[P], double rC, unsigned word, unsigned tab_addr) {
+    double d[U][P];
 #pragma unroll
-    for (int p = 0; p < P; ++p) {
-        if (ACC) {
-            const double t = __fma_rn(-2.0, x[p], 1.0);          // == fl(1 - fl(2x)): 2x is exact
-            const double d = __dmul_rn(r[p], fabs(t));           // == |r*(1-2x)| for r > 0
-            const unsigned hw = (unsigned)__double2hiint(d);
-            double hi, s;
-            lyap_log_core(hw, (unsigned)__double2loint(d), 0, tab, kTabCopies, &hi, &s);
-            lyap[p] = __dadd_rn(lyap[p], __dadd_rn(hi, s));
-            kemin[p] = min(kemin[p], (int)(hw >> 20));
+    for (int j = 0; j < U; ++j) {
+        const bool not_a = (word >> (2 * j)) & 1u;
+        const bool is_c = (word >> (2 * j + 1)) & 1u;
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+            double r = not_a ? rB[p] : rA[p];
+            if (HAS_C) r = is_c ? rC : r;
+            if (ACC) {
+                const double t = __fma_rn(-2.0, x[p], 1.0);      // == fl(1 - fl(2x)): 2x is exact
+                d[j][p] = __dmul_rn(r, fabs(t));                 // == |r*(1-2x)| for r > 0
+            }
+            x[p] = __dmul_rn(__dmul_rn(r, x[p]), __dsub_rn(1.0, x[p]));
         }
-        x[p] = __dmul_rn(__dmul_rn(r[p], x[p]), __dsub_rn(1.0, x[p]));
+    }
+    if (ACC) {
+        double z[U][P];
+        unsigned hw[U][P];
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+#pragma unroll
+            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, hw[j][p]);
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                lyap[p] = __dadd_rn(lyap[p], z[j][p]);
+                hwmin[p] = min(hwmin[p], hw[j][p]);              // a zero derivative leaves hw < 2^20
+            }
+        }
     }
 }
 
-template <int P, int THREADS>
+// U steps whose parameter choices are known at compile time (PAT: 2 bits per step, 0 = A, 1 = B, 2 = C):
+// no selects, no per-step branches; every operand is fixed.
+template <int P, bool ACC, int U, unsigned PAT>
+__device__ __forceinline__ void fixed_group(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P], const double (&rA)[P],
+                                            const double (&rB)[P], double rC, unsigned tab_addr) {
+    double d[U][P];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        const unsigned code = (PAT >> (2 * j)) & 3u;
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+            const double r = code == 0 ? rA[p] : (code == 1 ? rB[p] : rC);
+            if (ACC) {
+                const double t = __fma_rn(-2.0, x[p], 1.0);      // == fl(1 - fl(2x)): 2x is exact
+                d[j][p] = __dmul_rn(r, fabs(t));                 // == |r*(1-2x)| for r > 0
+            }
+            x[p] = __dmul_rn(__dmul_rn(r, x[p]), __dsub_rn(1.0, x[p]));
+        }
+    }
+    if (ACC) {
+        double z[U][P];
+        unsigned hw[U][P];
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+#pragma unroll
+            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, hw[j][p]);
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                lyap[p] = __dadd_rn(lyap[p], z[j][p]);
+                hwmin[p] = min(hwmin[p], hw[j][p]);
+            }
+        }
+    }
+}
+
+// 1 bit per step -> 2 bits per step (A/B patterns)
+__host__ __device__ constexpr unsigned spread_bits(unsigned m) {
+    return (m & 1u) | ((m & 2u) << 1) | ((m & 4u) << 2) | ((m & 8u) << 3);
+}
+
+// One group of U steps, dispatched on its pattern index to the matching straight-line body: one
+// warp-uniform multiway branch per U steps instead of a choice per step.
+//   !HAS_C: idx has one bit per step (0 = A, 1 = B), U is 2 or 4.   HAS_C: idx is the raw 2-bit codes, U is 2.
+template <int P, bool ACC, bool HAS_C, int U>
+__device__ __forceinline__ void dispatch_group(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P],
+                                               const double (&rA)[P], const double (&rB)[P], double rC, unsigned idx,
+                                               unsigned tab_addr) {
+#define LYAP_CASE_AB(N) \
+    case N: fixed_group<P, ACC, U, spread_bits(N)>(x, lyap, hwmin, rA, rB, rC, tab_addr); break;
+#define LYAP_CASE_RAW(N) \
+    case N: fixed_group<P, ACC, U, N>(x, lyap, hwmin, rA, rB, rC, tab_addr); break;
+    if (HAS_C) {
+        static_assert(!HAS_C || U == 2, "three-parameter groups are two steps long");
+        switch (idx) {
+            LYAP_CASE_RAW(0x0) LYAP_CASE_RAW(0x1) LYAP_CASE_RAW(0x2) LYAP_CASE_RAW(0x4) LYAP_CASE_RAW(0x5)
+            LYAP_CASE_RAW(0x6) LYAP_CASE_RAW(0x8) LYAP_CASE_RAW(0x9) LYAP_CASE_RAW(0xA)
+            default: break;   // code 3 is never produced by the host packing
+        }
+    } else if (U == 2) {
+        switch (idx) { LYAP_CASE_AB(0) LYAP_CASE_AB(1) LYAP_CASE_AB(2) LYAP_CASE_AB(3) default: break; }
+    } else {
+        switch (idx) {
+            LYAP_CASE_AB(0) LYAP_CASE_AB(1) LYAP_CASE_AB(2) LYAP_CASE_AB(3) LYAP_CASE_AB(4) LYAP_CASE_AB(5)
+            LYAP_CASE_AB(6) LYAP_CASE_AB(7) LYAP_CASE_AB(8) LYAP_CASE_AB(9) LYAP_CASE_AB(10) LYAP_CASE_AB(11)
+            LYAP_CASE_AB(12) LYAP_CASE_AB(13) LYAP_CASE_AB(14) LYAP_CASE_AB(15)
+            default: break;
+        }
+    }
+#undef LYAP_CASE_AB
+#undef LYAP_CASE_RAW
+}
+
+// even bits of w packed into the low 16 bits
+__device__ __forceinline__ unsigned compress_even_bits(unsigned w) {
+    w &= 0x55555555u;
+    w = (w | (w >> 1)) & 0x33333333u;
+    w = (w | (w >> 2)) & 0x0F0F0F0Fu;
+    w = (w | (w >> 4)) & 0x00FF00FFu;
+    w = (w | (w >> 8)) & 0x0000FFFFu;
+    return w;
+}
+
+// n steps of selector word `word` (2 bits per step: 0 = A, 1 = B, 2 = C).
+template <int P, bool ACC, bool HAS_C, int UNROLL>
+__device__ __forceinline__ void fast_chunk(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P], const double (&rA)[P],
+                                           const double (&rB)[P], double rC, unsigned word, int n, unsigned tab_addr) {
+    if (n == kStepsPerWord) {
+        constexpr int U = HAS_C ? 2 : UNROLL;
+        unsigned pat = HAS_C ? word : compress_even_bits(word);
+        constexpr int kBits = HAS_C ? 2 * U : U;
+#pragma unroll 1
+        for (int h = 0; h < kStepsPerWord / U; ++h) {
+            dispatch_group<P, ACC, HAS_C, U>(x, lyap, hwmin, rA, rB, rC, pat & ((1u << kBits) - 1u), tab_addr);
+            pat >>= kBits;
+        }
+    } else {
+#pragma unroll 1
+        for (int j = 0; j < n; ++j, word >>= 2) fast_group<P, ACC, HAS_C, 1>(x, lyap, hwmin, rA, rB, rC, word, tab_addr);
+    }
+}
+
+template <int P, int THREADS, bool HAS_C, int UNROLL>
 __global__ void __launch_bounds__(THREADS, 1)
 k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,
                unsigned long long* __restrict__ steps_out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     lyap_logtab_entry* tab_all = reinterpret_cast<lyap_logtab_entry*>(smem_raw);
-    for (int e = threadIdx.x; e < LYAP_LOG_BINS * kTabCopies; e += THREADS) tab_all[e] = g_lyap_logtab[e / kTabCopies];
+    for (int e = threadIdx.x; e < LYAP_LOG_BINS * kTabCopies; e += THREADS) {
+        lyap_logtab_entry t = g_lyap_logtab[e / kTabCopies];
+        t.invc = __hiloint2double(__double2hiint(t.invc) + 0x3FF00000, __double2loint(t.invc));   // see log_fast
+        tab_all[e] = t;
+    }
     __syncthreads();
     const lyap_logtab_entry* tab = tab_all + (threadIdx.x & (kTabCopies - 1));
+    const unsigned tab_addr = (unsigned)__cvta_generic_to_shared(tab);
 
     unsigned long long my_steps = 0;
     const long long tile_px = (long long)THREADS * P;
@@ -119,7 +285,8 @@ k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64,
 
     for (long long tile = blockIdx.x; tile * tile_px < a.n_pixels; tile += gridDim.x) {
         const long long idx0 = tile * tile_px + (long long)threadIdx.x * P;
-        double x[P], lyap[P], rA[P], rB[P], rC[P], lam[P];
+        double x[P], lyap[P], rA[P], rB[P], lam[P];
+        const double rC = a.c_value;
         int valid[P];
         bool done[P], careful_only[P];
 
@@ -132,7 +299,6 @@ k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64,
                 const bool inside = idx0 + p < a.n_pixels;
                 rB[p] = __dadd_rn(a.min_y, __dmul_rn(a.dy, (double)(int)row));   // :42
                 rA[p] = __dadd_rn(a.min_x, __dmul_rn(a.dx, (double)col));        // :45
-                rC[p] = a.c_value;
                 x[p] = 0.5;                                                       // :31,52
                 lyap[p] = 0.0;
                 valid[p] = 0;
@@ -160,40 +326,26 @@ k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64,
                 const unsigned word = a.sel[word0 + c];
                 const int n = min(kStepsPerWord, nsteps - c * kStepsPerWord);
                 double sx[P], sl[P];
-                int kemin[P];
+                unsigned hwmin[P];
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     sx[p] = x[p];
                     sl[p] = lyap[p];
-                    kemin[p] = 2047;
+                    hwmin[p] = 0x7FF00000u;
                 }
-                unsigned w = word;
-                if (acc) {
-                    for (int j = 0; j < n; ++j, w >>= 2) {
-                        const unsigned sel = w & 3u;
-                        if (sel == 0) fast_steps<P, true>(x, lyap, kemin, rA, tab);
-                        else if (sel == 1) fast_steps<P, true>(x, lyap, kemin, rB, tab);
-                        else fast_steps<P, true>(x, lyap, kemin, rC, tab);
-                    }
-                } else {
-                    for (int j = 0; j < n; ++j, w >>= 2) {
-                        const unsigned sel = w & 3u;
-                        if (sel == 0) fast_steps<P, false>(x, lyap, kemin, rA, tab);
-                        else if (sel == 1) fast_steps<P, false>(x, lyap, kemin, rB, tab);
-                        else fast_steps<P, false>(x, lyap, kemin, rC, tab);
-                    }
-                }
+                if (acc) fast_chunk<P, true, HAS_C, UNROLL>(x, lyap, hwmin, rA, rB, rC, word, n, tab_addr);
+                else fast_chunk<P, false, HAS_C, UNROLL>(x, lyap, hwmin, rA, rB, rC, word, n, tab_addr);
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     if (done[p]) continue;
-                    const bool regular = !careful_only[p] && in_unit_interval(x[p]) && kemin[p] != 0;
+                    const bool regular = !careful_only[p] && in_unit_interval(x[p]) && hwmin[p] >= 0x00100000u;
                     if (regular) {
                         if (acc) valid[p] += n;
                         my_steps += (unsigned long long)n;
                     } else {
                         PixelState ps{sx[p], sl[p], valid[p]};
-                        const bool dead = acc ? careful_chunk<true>(&ps, rA[p], rB[p], rC[p], word, n, tab, &my_steps)
-                                              : careful_chunk<false>(&ps, rA[p], rB[p], rC[p], word, n, tab, &my_steps);
+                        const bool dead = acc ? careful_chunk<true>(&ps, rA[p], rB[p], rC, word, n, &my_steps)
+                                              : careful_chunk<false>(&ps, rA[p], rB[p], rC, word, n, &my_steps);
                         x[p] = ps.x;
                         lyap[p] = ps.lyap;
                         valid[p] = ps.valid;
@@ -245,29 +397,48 @@ k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64,
     }
 }
 
-constexpr int kExactP = 2;
-constexpr int kExactThreads = 512;
-
-cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
-                                int sm_count, cudaStream_t st) {
-    auto kern = k_lambda_exact<kExactP, kExactThreads>;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+template <int P, int THREADS, bool HAS_C, int UNROLL>
+static cudaError_t launch_exact_variant(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                        int sm_count, cudaStream_t st) {
+    auto kern = k_lambda_exact<P, THREADS, HAS_C, UNROLL>;
+    // the attribute is per device and cheap to set; doing it on every launch keeps this thread- and device-safe
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTabSmemBytes);
     if (e != cudaSuccess) return e;
-    if (dev < 64 && !attr_set[dev]) {
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTabSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
-    }
-    const long long tile_px = (long long)kExactThreads * kExactP;
+    const long long tile_px = (long long)THREADS * P;
     const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) return cudaSuccess;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    kern<<<grid, kExactThreads, kTabSmemBytes, st>>>(a, out64, out32, steps);
+    kern<<<grid, THREADS, kTabSmemBytes, st>>>(a, out64, out32, steps);
     return cudaGetLastError();
 }
 
+static int exact_variant_from_env() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("LYAP_EXACT_VARIANT");   // tuning knob for experiments; default 0
+        v = e ? atoi(e) : 0;
+    }
+    return v;
+}
+
+cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                int sm_count, cudaStream_t st) {
+    bool has_c = false;
+    const int words = a.acc_word0 + (a.iterations + kStepsPerWord - 1) / kStepsPerWord;
+    for (int i = 0; i < words; ++i) has_c = has_c || (a.sel[i] & 0xAAAAAAAAu);
+#define LYAP_VARIANT(P, T, U)                                                                    \
+    (has_c ? launch_exact_variant<P, T, true, U>(a, out64, out32, steps, sm_count, st)            \
+           : launch_exact_variant<P, T, false, U>(a, out64, out32, steps, sm_count, st))
+    switch (exact_variant_from_env()) {
+        default:
+        case 0: return LYAP_VARIANT(3, 512, 2);   // measured best on B200 (4096^2 "AABAB")
+        case 1: return LYAP_VARIANT(2, 512, 2);
+        case 2: return LYAP_VARIANT(2, 512, 4);
+        case 3: return LYAP_VARIANT(4, 512, 2);
+        case 4: return LYAP_VARIANT(2, 1024, 2);
+    }
+#undef LYAP_VARIANT
+}
 
 // ---------------------------------------------------------------------------------------------
 // normalizeData pass 1: min / max over finite values > -4.
