@@ -155,6 +155,24 @@ int lyap_colorize(lyap_ctx* ctx, const double* norm, int32_t width, int32_t heig
 int lyap_render(lyap_ctx* ctx, const lyap_params* p, double* out_lambda, float* out_lambda32, double* out_norm,
                 uint8_t* out_rgba, lyap_progress_fn progress, lyap_render_stats* stats);
 
+/* ---- for callers that must not allocate ---- */
+
+/* No counterpart in the reference.  Same result as lyap_minmax_device, for hosts that are not allowed to
+ * allocate device memory at the time of the call: a renderer that fixed its memory budget at start-up, code
+ * running between frames of a real-time loop where an allocation may stall the whole device, or a plug-in whose
+ * host forbids driver allocations after initialisation.  It needs no lyap_ctx (creating one allocates): it runs on
+ * the CURRENT device, on the given cudaStream_t (NULL = default stream), and its reduction scratch is a fixed
+ * array inside the library image (about 19 KB, resident on every GPU that loads the library until exit).
+ * It calls no cudaMalloc / cudaFree and no allocating routine.
+ *   - n may be at most LYAP_NOALLOC_MAX_VALUES; larger sizes return LYAP_ERR_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address (one-time set-up); make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array: calls that may overlap on the GPU (different streams,
+ *     different threads) race and give wrong results; order them on one stream or with events.
+ *   - d_values / d_minmax are device pointers supplied by the caller; only enqueues work. */
+#define LYAP_NOALLOC_MAX_VALUES (1ull << 32)
+int lyap_minmax_device_noalloc(const double* d_values, uint64_t n, double* d_minmax, void* cuda_stream);
+
 /* ---- measurement ---- */
 
 /* Issue-rate micro-benchmark of the fp64 pipe on the context's device: independent DFMA chains,

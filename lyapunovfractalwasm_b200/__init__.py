@@ -84,6 +84,7 @@ ABI = {
     "lyap_colorize": (ctypes.c_int, [_P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _P]),
     "lyap_render": (ctypes.c_int, [_P, ctypes.POINTER(LyapParams), _P, _P, _P, _P, _P,
                                    ctypes.POINTER(RenderStats)]),
+    "lyap_minmax_device_noalloc": (ctypes.c_int, [_P, ctypes.c_uint64, _P, _P]),
     "lyap_fp64_peak": (ctypes.c_int, [_P, c_double_p]),
     "lyap_fp32_peak": (ctypes.c_int, [_P, c_double_p]),
 }
@@ -129,6 +130,14 @@ def make_params(min_x=0.0, max_x=4.0, min_y=0.0, max_y=4.0, width=800, height=60
     p.c_value = 0.0 if c is None else c
     p.row_begin, p.row_end = row_begin, row_end
     return p
+
+
+NOALLOC_MAX_VALUES = 1 << 32
+
+
+def minmax_device_noalloc(d_values, n, d_minmax, cuda_stream=None):
+    """lyap_minmax_device_noalloc on the current device: no context, no allocation (see include/lyap_b200.h)."""
+    _check(load_library().lyap_minmax_device_noalloc(d_values, n, d_minmax, cuda_stream))
 
 
 class DeviceBuffer:

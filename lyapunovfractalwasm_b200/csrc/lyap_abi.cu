@@ -154,6 +154,10 @@ int check_ctx(lyap_ctx* c) {
 
 }  // namespace
 
+namespace lyap {
+int set_error(int status, const char* message) { return fail(status, message); }
+}  // namespace lyap
+
 extern "C" {
 
 int lyap_abi_version(void) { return LYAP_ABI_VERSION; }

@@ -48,4 +48,7 @@ cudaError_t launch_colorize(const double* norm, int width, long long rows, int r
 cudaError_t launch_fp64_peak(double* sink, int sm_count, int iters, unsigned long long* instr, cudaStream_t st);
 cudaError_t launch_fp32_peak(float* sink, int sm_count, int iters, unsigned long long* instr, cudaStream_t st);
 
+// records the calling thread's last error message (implemented beside lyap_last_error)
+int set_error(int status, const char* message);
+
 }  // namespace lyap

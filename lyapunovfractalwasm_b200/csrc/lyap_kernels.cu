@@ -538,6 +538,57 @@ cudaError_t launch_minmax(const double* v, unsigned long long n, double* minmax,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Min/max without any allocation (lyap_minmax_device_noalloc in the public header).
+//
+// Same kernel as above; its scratch (per-block partial results and the arrival ticket) is this fixed
+// array in the library image instead of memory owned by a context.  In host code the array's name is
+// only a handle: the address a kernel can use is obtained once per device with cudaGetSymbolAddress,
+// with that device current, and cached.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_minmax_fixed_scratch[(kMinmaxScratchBytes + 255) / 256 * 256];
+
+}  // namespace lyap
+
+#include <mutex>
+
+#include "../../include/lyap_b200.h"
+
+extern "C" int lyap_minmax_device_noalloc(const double* d_values, uint64_t n, double* d_minmax, void* cuda_stream) {
+    using namespace lyap;
+    if (!d_minmax || (!d_values && n)) return set_error(LYAP_ERR_INVALID, "lyap_minmax_device_noalloc: null pointer");
+    if (n > LYAP_NOALLOC_MAX_VALUES)
+        return set_error(LYAP_ERR_TOO_LARGE, "lyap_minmax_device_noalloc: n exceeds LYAP_NOALLOC_MAX_VALUES (2^32 values)");
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static void* scratch_of_device[kMaxDevices] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return set_error(LYAP_ERR_INVALID, "lyap_minmax_device_noalloc: device ordinal out of range");
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!scratch_of_device[dev]) {   // one-time set-up for this device (it is the current one)
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_minmax_fixed_scratch);
+            if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
+            scratch_of_device[dev] = p;
+        }
+        scratch = scratch_of_device[dev];
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    // the arrival ticket must start at zero; the array keeps whatever the last call (or an aborted one) left
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(static_cast<double*>(scratch) + 2 * kMinmaxBlocks);
+    e = cudaMemsetAsync(ticket, 0, 16, st);
+    if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
+    e = launch_minmax(d_values, n, d_minmax, scratch, st);
+    if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
+    return LYAP_OK;
+}
+
+namespace lyap {
+
+// ---------------------------------------------------------------------------------------------
 // normalizeData pass 2.
 // ---------------------------------------------------------------------------------------------
 constexpr int kNormThreads = 256;
