@@ -94,6 +94,7 @@ struct LogConsts {
     double c2, c3, c4, ln2hi, ln2lo, klo_bias;
 };
 __constant__ LogConsts c_logk = {LYAP_LOG_C2, LYAP_LOG_C3, LYAP_LOG_C4, LYAP_LN2HI, LYAP_LN2LO, LYAP_KLO_BIAS};
+__constant__ int c_minus_2p20 = -(1 << 20);   // read as a constant-bank operand so the product below stays one multiply-add
 
 // lyap_log_core (lyap_math.h) for a positive normal d, written against the interleaved shared-memory
 // table: `tab_addr` is the shared-window byte address of this lane's copy of entry 0, entries are
@@ -107,8 +108,11 @@ __device__ __forceinline__ double log_fast(double d, unsigned tab_addr, unsigned
     // The shared copy holds invc with 0x3FF00000 added to its high word, so subtracting d's exponent field
     // gives invc * 2^-(exponent of d): d * that == mantissa(d) * invc exactly (a power-of-two rescaling),
     // without assembling the mantissa as a separate double.
-    const double invs = __hiloint2double(__double2hiint(invcb) - (int)(hw & 0xFFF00000u), __double2loint(invcb));
-    const double kd = (double)(int)(hw >> 20);
+    const int ke = (int)(hw >> 20);
+    int invs_hi;
+    asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(invs_hi) : "r"(ke), "r"(c_minus_2p20), "r"(__double2hiint(invcb)));
+    const double invs = __hiloint2double(invs_hi, __double2loint(invcb));
+    const double kd = (double)ke;
     const double r = __fma_rn(d, invs, -1.0);
     double q = __fma_rn(r, c_logk.c4, c_logk.c3);
     q = __fma_rn(r, q, c_logk.c2);
@@ -222,7 +226,13 @@ __device__ __forceinline__ void dispatch_group(double (&x)[P], double (&lyap)[P]
             default: break;   // code 3 is never produced by the host packing
         }
     } else if (U == 2) {
-        switch (idx) { LYAP_CASE_AB(0) LYAP_CASE_AB(1) LYAP_CASE_AB(2) LYAP_CASE_AB(3) default: break; }
+        if (idx & 1u) {
+            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(3)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
+            else fixed_group<P, ACC, U, spread_bits(1)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
+        } else {
+            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(2)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
+            else fixed_group<P, ACC, U, spread_bits(0)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
+        }
     } else {
         switch (idx) {
             LYAP_CASE_AB(0) LYAP_CASE_AB(1) LYAP_CASE_AB(2) LYAP_CASE_AB(3) LYAP_CASE_AB(4) LYAP_CASE_AB(5)
