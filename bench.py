@@ -164,6 +164,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--mode", default="exact", choices=["exact", "fast64", "fast32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gather", action="store_true", help="skip the optional NCCL gather of the RGBA bands to rank 0 (N > 1)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -299,6 +300,23 @@ def main():
         dist.all_reduce(s, op=dist.ReduceOp.SUM)
     e2e_value = int(s[0]) / (float(t[0]) * 1e-3)
 
+    # ---- optional: gather the finished RGBA bands to rank 0 over NCCL (outside the timed regions above) ----
+    gather = None
+    if dist is not None and not args.no_gather:
+        parts = [torch.empty_like(d_rgba) for _ in range(world)] if rank == 0 else None
+        dist.gather(d_rgba, parts, dst=0)          # warm-up (connection set-up)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        dist.gather(d_rgba, parts, dst=0)
+        g1.record(stream)
+        torch.cuda.synchronize()
+        tg = torch.tensor([g0.elapsed_time(g1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        nbytes = d_rgba.numel() * (world - 1)
+        gather = {"ms": float(tg[0]), "bytes_into_rank0": nbytes, "gbs": nbytes / (float(tg[0]) * 1e-3) / 1e9,
+                  "what": "torch.distributed.gather (NCCL) of each rank's RGBA8 band into rank 0's memory, timed apart from the steps"}
+
     if rank == 0:
         hbm_peak = None
         try:
@@ -348,6 +366,8 @@ def main():
             "gpu_launches": 4 * args.steps,
             "clocks": clocks,
         }
+        if gather is not None:
+            line["gather"] = gather
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_leg()
         print(json.dumps(line), flush=True)
