@@ -155,6 +155,18 @@ int lyap_colorize(lyap_ctx* ctx, const double* norm, int32_t width, int32_t heig
 int lyap_render(lyap_ctx* ctx, const lyap_params* p, double* out_lambda, float* out_lambda32, double* out_norm,
                 uint8_t* out_rgba, lyap_progress_fn progress, lyap_render_stats* stats);
 
+/* One frame over several devices of this machine, from one process (one worker thread and one context per
+ * entry of `devices`; the same ordinal may appear more than once).  Rows are split into contiguous bands
+ * (reference rows loop, src/lyapunov_fractal.hpp:41); each band recomputes one halo row per inner side for the
+ * 3x3 mean; the only exchange is the frame's min/max (normalizeData, :110-125), done on the host.  Every band
+ * is copied into its place in the host buffers (any may be NULL), so the result is byte-identical to
+ * lyap_render on one device.  If a worker does not reach the exchange within timeout_seconds (<= 0: 60 s) the
+ * call returns LYAP_ERR_TIMEOUT once the workers that did arrive have stopped; a negative ordinal in
+ * `devices` stands for a worker that never arrives (used by the tests to exercise that path without
+ * disturbing a GPU).  stats->ms_total_device is the wall-clock time of the whole call here. */
+int lyap_render_multi(const lyap_params* p, int32_t n_devices, const int32_t* devices, double* out_lambda,
+                      double* out_norm, uint8_t* out_rgba, double timeout_seconds, lyap_render_stats* stats);
+
 /* ---- for callers that must not allocate ---- */
 
 /* No counterpart in the reference.  Same result as lyap_minmax_device, for hosts that are not allowed to

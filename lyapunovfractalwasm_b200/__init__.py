@@ -84,6 +84,8 @@ ABI = {
     "lyap_colorize": (ctypes.c_int, [_P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _P]),
     "lyap_render": (ctypes.c_int, [_P, ctypes.POINTER(LyapParams), _P, _P, _P, _P, _P,
                                    ctypes.POINTER(RenderStats)]),
+    "lyap_render_multi": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), _P, _P,
+                                         _P, ctypes.c_double, ctypes.POINTER(RenderStats)]),
     "lyap_minmax_device_noalloc": (ctypes.c_int, [_P, ctypes.c_uint64, _P, _P]),
     "lyap_fp64_peak": (ctypes.c_int, [_P, c_double_p]),
     "lyap_fp32_peak": (ctypes.c_int, [_P, c_double_p]),
@@ -138,6 +140,24 @@ NOALLOC_MAX_VALUES = 1 << 32
 def minmax_device_noalloc(d_values, n, d_minmax, cuda_stream=None):
     """lyap_minmax_device_noalloc on the current device: no context, no allocation (see include/lyap_b200.h)."""
     _check(load_library().lyap_minmax_device_noalloc(d_values, n, d_minmax, cuda_stream))
+
+
+def render_multi(params, devices, want=("lambda", "norm", "rgba"), timeout_seconds=0.0):
+    """lyap_render_multi: one frame over the listed device ordinals, from this process."""
+    h, w = params.height, params.width
+    out, ptrs = {}, {}
+    for key, dtype, shape in (("lambda", np.float64, (h, w)), ("norm", np.float64, (h, w)), ("rgba", np.uint8, (h, w, 4))):
+        if key in want:
+            out[key] = np.empty(shape, dtype=dtype)
+            ptrs[key] = out[key].ctypes.data
+        else:
+            ptrs[key] = None
+    devs = (ctypes.c_int32 * len(devices))(*devices)
+    stats = RenderStats()
+    _check(load_library().lyap_render_multi(ctypes.byref(params), len(devices), devs, ptrs["lambda"], ptrs["norm"],
+                                            ptrs["rgba"], timeout_seconds, ctypes.byref(stats)))
+    out["stats"] = stats
+    return out
 
 
 class DeviceBuffer:

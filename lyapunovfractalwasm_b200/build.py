@@ -45,6 +45,19 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+CLI = os.path.join(HERE, "lyap_cli")
+
+
+def build_cli(force=False):
+    """The C++23 command-line driver (host code only; links the engine library)."""
+    src = os.path.join(CSRC, "lyap_cli.cpp")
+    if not force and not _newer(CLI, [src, os.path.join(ROOT, "include", "lyap_b200.h"), LIB]):
+        return CLI
+    subprocess.run(["g++", "-std=c++23", "-O2", "-Wall", "-o", CLI, src, "-L", HERE, "-llyap_b200",
+                    "-Wl,-rpath,$ORIGIN"], check=True)
+    return CLI
+
+
 def build_oracle():
     """Compile the CPU checkers (test infrastructure).  Uses the reference sources only where present."""
     subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle")], check=True)
@@ -52,5 +65,6 @@ def build_oracle():
 
 if __name__ == "__main__":
     build_library(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    build_cli(force="--force" in sys.argv)
     build_oracle()
     print(LIB)

@@ -6,7 +6,11 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <chrono>
+#include <condition_variable>
+#include <mutex>
 #include <new>
+#include <thread>
 #include <string>
 #include <vector>
 
@@ -518,6 +522,153 @@ int lyap_colorize(lyap_ctx* c, const double* norm, int32_t width, int32_t height
     CU(cudaStreamSynchronize(st));
     return LYAP_OK;
 }
+
+}  // extern "C"
+
+// ---- one frame over several devices ----
+
+namespace {
+
+struct MultiShared {
+    std::mutex mu;
+    std::condition_variable cv;
+    int arrived = 0, expected = 0;
+    bool failed = false;
+    double lo = 0, hi = 0;
+    bool have = false;
+    unsigned long long steps = 0;
+    int status = LYAP_OK;
+    std::string error;
+};
+
+void multi_fail(MultiShared& sh, int status, const char* msg) {
+    std::lock_guard<std::mutex> lk(sh.mu);
+    if (sh.status == LYAP_OK) {
+        sh.status = status;
+        sh.error = msg;
+    }
+    sh.failed = true;
+    sh.cv.notify_all();
+}
+
+// One band on one device.  Returns after its part of the host buffers is written, or after a failure anywhere.
+void multi_worker(MultiShared& sh, const lyap_params& base, int device, long long b0, long long b1, double* out_lambda,
+                  double* out_norm, uint8_t* out_rgba, double timeout_s) {
+    lyap_ctx* c = nullptr;
+    if (lyap_create(&c, device) != LYAP_OK) return multi_fail(sh, LYAP_ERR_CUDA, lyap_last_error());
+    const long long H = base.height, W = base.width;
+    const int above = b0 > 0 ? 1 : 0, below = b1 < H ? 1 : 0;
+    const long long rows_all = (b1 - b0) + above + below, rows_own = b1 - b0;
+    void *d_lam = nullptr, *d_norm = nullptr, *d_rgba = nullptr, *d_small = nullptr;
+    auto cleanup = [&]() {
+        for (void* q : {d_lam, d_norm, d_rgba, d_small})
+            if (q) lyap_device_free(c, q);
+        lyap_destroy(c);
+    };
+    auto bail = [&](int st) {
+        multi_fail(sh, st, lyap_last_error());
+        cleanup();
+    };
+    const bool colour = out_norm || out_rgba;
+    int st = lyap_device_alloc(c, &d_lam, (size_t)rows_all * W * 8);
+    if (st == LYAP_OK) st = lyap_device_alloc(c, &d_small, 32);
+    if (st == LYAP_OK && colour) st = lyap_device_alloc(c, &d_norm, (size_t)rows_all * W * 8);
+    if (st == LYAP_OK && out_rgba) st = lyap_device_alloc(c, &d_rgba, (size_t)rows_own * W * 4);
+    if (st != LYAP_OK) return bail(st);
+    double* d_mm = static_cast<double*>(d_small);
+    uint64_t* d_steps = reinterpret_cast<uint64_t*>(d_mm + 2);
+    uint64_t zero = 0;
+    lyap_params p = base;
+    p.row_begin = b0 - above;
+    p.row_end = b1 + below;
+    double* own = static_cast<double*>(d_lam) + (size_t)above * W;
+    st = lyap_copy_to_device(c, d_steps, &zero, 8);
+    if (st == LYAP_OK) st = lyap_lambda_device(c, &p, static_cast<double*>(d_lam), nullptr, d_steps);
+    if (st == LYAP_OK) st = lyap_minmax_device(c, own, (uint64_t)rows_own * W, d_mm);
+    double mm[2];
+    uint64_t steps = 0;
+    if (st == LYAP_OK) st = lyap_copy_to_host(c, mm, d_mm, 16);
+    if (st == LYAP_OK) st = lyap_copy_to_host(c, &steps, d_steps, 8);
+    if (st != LYAP_OK) return bail(st);
+    // halo rows were computed too; count only the band's own share of the steps
+    steps = steps / (uint64_t)rows_all * (uint64_t)rows_own + steps % (uint64_t)rows_all * (uint64_t)rows_own / (uint64_t)rows_all;
+    {   // the one exchange: min of mins, max of maxes, with a deadline
+        std::unique_lock<std::mutex> lk(sh.mu);
+        sh.lo = sh.have ? std::fmin(sh.lo, mm[0]) : mm[0];
+        sh.hi = sh.have ? std::fmax(sh.hi, mm[1]) : mm[1];
+        sh.have = true;
+        sh.steps += steps;
+        ++sh.arrived;
+        sh.cv.notify_all();
+        const bool ok = sh.cv.wait_for(lk, std::chrono::duration<double>(timeout_s),
+                                       [&] { return sh.arrived == sh.expected || sh.failed; });
+        if (!ok && sh.status == LYAP_OK) {
+            sh.status = LYAP_ERR_TIMEOUT;
+            sh.error = "lyap_render_multi: a band did not reach the min/max exchange before the deadline";
+            sh.failed = true;
+            sh.cv.notify_all();
+        }
+        if (sh.failed) {
+            lk.unlock();
+            cleanup();
+            return;
+        }
+        mm[0] = sh.lo;
+        mm[1] = sh.hi;
+    }
+    if (out_lambda) st = lyap_copy_to_host(c, out_lambda + (size_t)b0 * W, own, (size_t)rows_own * W * 8);
+    if (st == LYAP_OK && colour) {
+        st = lyap_copy_to_device(c, d_mm, mm, 16);
+        if (st == LYAP_OK) st = lyap_normalize_device(c, static_cast<double*>(d_lam), (uint64_t)rows_all * W, d_mm, static_cast<double*>(d_norm));
+        double* norm_own = static_cast<double*>(d_norm) + (size_t)above * W;
+        if (st == LYAP_OK && out_rgba)
+            st = lyap_colorize_device(c, norm_own, base.width, rows_own, above, below, base.palette, static_cast<uint8_t*>(d_rgba));
+        if (st == LYAP_OK && out_norm) st = lyap_copy_to_host(c, out_norm + (size_t)b0 * W, norm_own, (size_t)rows_own * W * 8);
+        if (st == LYAP_OK && out_rgba) st = lyap_copy_to_host(c, out_rgba + (size_t)b0 * W * 4, d_rgba, (size_t)rows_own * W * 4);
+    }
+    if (st != LYAP_OK) return bail(st);
+    cleanup();
+}
+
+}  // namespace
+
+extern "C" int lyap_render_multi(const lyap_params* p, int32_t n_devices, const int32_t* devices, double* out_lambda,
+                                 double* out_norm, uint8_t* out_rgba, double timeout_seconds, lyap_render_stats* stats) {
+    lyap::LambdaArgs args;
+    Geometry g;
+    if (int r = build_args(p, &args, &g)) return r;
+    if (g.rows != p->height) return fail(LYAP_ERR_INVALID, "lyap_render_multi renders whole frames (row_begin = row_end = 0)");
+    if (n_devices < 1 || !devices) return fail(LYAP_ERR_INVALID, "need at least one device");
+    if (n_devices > p->height) return fail(LYAP_ERR_INVALID, "more bands than rows");
+    if (timeout_seconds <= 0) timeout_seconds = 60.0;
+    const auto t0 = std::chrono::steady_clock::now();
+    MultiShared sh;
+    sh.expected = n_devices;
+    std::vector<std::thread> workers;
+    const long long H = p->height, base = H / n_devices, extra = H % n_devices;
+    for (int r = 0; r < n_devices; ++r) {
+        const long long b0 = r * base + (r < extra ? r : extra);
+        const long long b1 = b0 + base + (r < extra ? 1 : 0);
+        if (devices[r] < 0) continue;   // a band whose worker never arrives
+        workers.emplace_back(multi_worker, std::ref(sh), std::cref(*p), (int)devices[r], b0, b1, out_lambda, out_norm,
+                             out_rgba, timeout_seconds);
+    }
+    for (auto& w : workers) w.join();
+    if (workers.empty()) return fail(LYAP_ERR_TIMEOUT, "lyap_render_multi: no band arrived");
+    if (sh.status != LYAP_OK) return fail(sh.status, sh.error);
+    if (stats) {
+        std::memset(stats, 0, sizeof(*stats));
+        stats->executed_steps = sh.steps;
+        stats->nominal_steps = (uint64_t)g.n_pixels * (uint64_t)((long long)p->warmup + p->iterations);
+        stats->lambda_min = sh.lo;
+        stats->lambda_max = sh.hi;
+        stats->ms_total_device = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        stats->kernel_launches = 4 * n_devices;
+    }
+    return LYAP_OK;
+}
+
+extern "C" {
 
 // ---- measurement ----
 

@@ -1,0 +1,162 @@
+// lyap_cli.cpp -- command-line driver over the C ABI (C++23 host code, no CUDA in this file).
+//
+// Default arguments reproduce the page's own call (reference web/fractal_renderer.js:144-154):
+// 800x800, a,b in [0,4], warm-up 100, sequence and iteration count as the form would give them
+// (web/index.html:110-124; defaults "AB", 1000), palette "cosmic".  --config N selects one of the five
+// benchmark configurations.  Output: one JSON line with timings; --out writes the frame (.ppm = RGB,
+// .rgba = raw RGBA8, .f64 = raw normalised doubles, the array the WASM export returns).
+#include <charconv>
+#include <chrono>
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <format>
+#include <fstream>
+#include <iostream>
+#include <string>
+#include <string_view>
+#include <vector>
+
+#include "../../include/lyap_b200.h"
+
+namespace {
+
+struct Options {
+    double min_x = 0.0, max_x = 4.0, min_y = 0.0, max_y = 4.0;
+    int width = 800, height = 800, iterations = 1000, warmup = 100;
+    std::string sequence = "AB", palette = "cosmic", mode = "exact", out;
+    bool has_c = false;
+    double c = 0.0;
+    int gpus = 1, frame = 0;
+};
+
+[[noreturn]] void usage(const char* why) {
+    std::cerr << "lyap_cli: " << why << "\n"
+              << "usage: lyap_cli [--config 1..5 [--frame K]] [--width W --height H --min-x .. --max-x .. --min-y .. --max-y ..]\n"
+              << "                [--sequence S] [--iterations N] [--warmup N] [--c V] [--palette NAME]\n"
+              << "                [--mode exact|fast64|fast32] [--gpus N] [--out file.ppm|.rgba|.f64]\n";
+    std::exit(2);
+}
+
+void apply_config(Options& o, int n) {
+    switch (n) {
+        case 1: o = {2, 4, 2, 4, 512, 512, 1000, 100, "AB"}; break;
+        case 2: o = {2.5, 4, 2.5, 4, 4096, 4096, 2000, 200, "AABAB"}; break;
+        case 3: o = {3.4, 4.0, 2.5, 3.4, 16384, 16384, 4000, 500, "BBBBBBAAAAAA"}; break;
+        case 4: o = {2, 4, 2, 4, 65536, 65536, 1000, 100, "AB"}; break;
+        case 5: {
+            const int k = o.frame;
+            const double h = 0.5 * std::pow(0.97, k);   // zoom batch: half-width 0.5*0.97^k around (3.82, 3.45)
+            o = {3.82 - h, 3.82 + h, 3.45 - h, 3.45 + h, 1920, 1080, 3000, 300, "ABC"};
+            o.has_c = true;
+            o.c = 3.7;
+            o.frame = k;
+        } break;
+        default: usage("--config takes 1..5");
+    }
+}
+
+double to_double(std::string_view s) {
+    return std::strtod(std::string(s).c_str(), nullptr);
+}
+
+int to_int(std::string_view s) {
+    int v = 0;
+    auto [p, ec] = std::from_chars(s.data(), s.data() + s.size(), v);
+    if (ec != std::errc() || p != s.data() + s.size()) usage("bad integer");
+    return v;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+    Options o;
+    std::vector<std::string_view> args(argv + 1, argv + argc);
+    // --frame has to be known before --config 5 is applied
+    for (size_t i = 0; i + 1 < args.size(); ++i)
+        if (args[i] == "--frame") o.frame = to_int(args[i + 1]);
+    for (size_t i = 0; i < args.size(); ++i) {
+        const auto a = args[i];
+        auto next = [&]() -> std::string_view {
+            if (i + 1 >= args.size()) usage("missing value");
+            return args[++i];
+        };
+        if (a == "--config") { const int fr = o.frame; o.frame = fr; apply_config(o, to_int(next())); }
+        else if (a == "--frame") next();
+        else if (a == "--width") o.width = to_int(next());
+        else if (a == "--height") o.height = to_int(next());
+        else if (a == "--min-x") o.min_x = to_double(next());
+        else if (a == "--max-x") o.max_x = to_double(next());
+        else if (a == "--min-y") o.min_y = to_double(next());
+        else if (a == "--max-y") o.max_y = to_double(next());
+        else if (a == "--sequence") o.sequence = std::string(next());
+        else if (a == "--iterations") o.iterations = to_int(next());
+        else if (a == "--warmup") o.warmup = to_int(next());
+        else if (a == "--c") { o.has_c = true; o.c = to_double(next()); }
+        else if (a == "--palette") o.palette = std::string(next());
+        else if (a == "--mode") o.mode = std::string(next());
+        else if (a == "--gpus") o.gpus = to_int(next());
+        else if (a == "--out") o.out = std::string(next());
+        else usage("unknown option");
+    }
+
+    lyap_params p;
+    lyap_params_default(&p);
+    p.min_x = o.min_x; p.max_x = o.max_x; p.min_y = o.min_y; p.max_y = o.max_y;
+    p.width = o.width; p.height = o.height;
+    p.sequence = o.sequence.data(); p.sequence_len = static_cast<int32_t>(o.sequence.size());
+    p.iterations = o.iterations; p.warmup = o.warmup;
+    p.mode = o.mode == "exact" ? LYAP_MODE_EXACT : o.mode == "fast64" ? LYAP_MODE_FAST_FP64 : o.mode == "fast32" ? LYAP_MODE_FAST_FP32 : -1;
+    if (p.mode < 0) usage("--mode takes exact, fast64 or fast32");
+    p.palette = lyap_palette_from_name(o.palette.c_str());
+    p.c_enabled = o.has_c ? 1 : 0;
+    p.c_value = o.c;
+
+    const size_t n = static_cast<size_t>(o.width) * static_cast<size_t>(o.height);
+    const bool want_f64 = o.out.ends_with(".f64");
+    std::vector<double> norm(want_f64 ? n : 0);
+    std::vector<uint8_t> rgba(n * 4);
+    lyap_render_stats st{};
+    const auto t0 = std::chrono::steady_clock::now();
+    int status;
+    if (o.gpus <= 1) {
+        lyap_ctx* ctx = nullptr;
+        if ((status = lyap_create(&ctx, 0)) == LYAP_OK) {
+            status = lyap_render(ctx, &p, nullptr, nullptr, want_f64 ? norm.data() : nullptr, rgba.data(),
+                                 [](double f) { std::fprintf(stderr, "\rprogress %5.1f %%", 100.0 * f); }, &st);
+            std::fprintf(stderr, "\n");
+            lyap_destroy(ctx);
+        }
+    } else {
+        std::vector<int32_t> devs(o.gpus);
+        for (int i = 0; i < o.gpus; ++i) devs[i] = i;
+        status = lyap_render_multi(&p, o.gpus, devs.data(), nullptr, want_f64 ? norm.data() : nullptr, rgba.data(), 0.0, &st);
+    }
+    const double wall_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (status != LYAP_OK) {
+        std::cerr << "lyap_cli: " << lyap_status_string(status) << ": " << lyap_last_error() << "\n";
+        return 1;
+    }
+    if (!o.out.empty()) {
+        std::ofstream f(o.out, std::ios::binary);
+        if (!f) { std::cerr << "lyap_cli: cannot write " << o.out << "\n"; return 1; }
+        if (o.out.ends_with(".ppm")) {
+            f << std::format("P6\n{} {}\n255\n", o.width, o.height);
+            std::vector<uint8_t> rgb(n * 3);
+            for (size_t i = 0; i < n; ++i) { rgb[3 * i] = rgba[4 * i]; rgb[3 * i + 1] = rgba[4 * i + 1]; rgb[3 * i + 2] = rgba[4 * i + 2]; }
+            f.write(reinterpret_cast<const char*>(rgb.data()), static_cast<std::streamsize>(rgb.size()));
+        } else if (want_f64) {
+            f.write(reinterpret_cast<const char*>(norm.data()), static_cast<std::streamsize>(n * 8));
+        } else {
+            f.write(reinterpret_cast<const char*>(rgba.data()), static_cast<std::streamsize>(rgba.size()));
+        }
+    }
+    std::cout << std::format(
+        "{{\"width\": {}, \"height\": {}, \"sequence\": \"{}\", \"mode\": \"{}\", \"gpus\": {}, \"executed_steps\": {}, "
+        "\"nominal_steps\": {}, \"lambda_min\": {}, \"lambda_max\": {}, \"ms_lambda\": {:.3f}, \"ms_device\": {:.3f}, "
+        "\"ms_wall\": {:.3f}, \"steps_per_s_wall\": {:.4e}}}\n",
+        o.width, o.height, o.sequence, o.mode, o.gpus, st.executed_steps, st.nominal_steps, st.lambda_min, st.lambda_max,
+        st.ms_lambda, st.ms_total_device, wall_ms, st.executed_steps / (wall_ms * 1e-3));
+    return 0;
+}

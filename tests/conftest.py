@@ -17,6 +17,7 @@ def built():
     """Make sure the engine library and the CPU checkers exist (compiles them where a toolchain is present)."""
     from lyapunovfractalwasm_b200 import build
     build.build_library()
+    build.build_cli()
     build.build_oracle()
 
 

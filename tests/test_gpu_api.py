@@ -126,3 +126,54 @@ def test_fast_modes_within_stated_tolerance(engine):
 def test_peak_microbenchmarks_report_plausible_rates(engine):
     f64, f32 = engine.fp64_peak(), engine.fp32_peak()
     assert 5e12 < f64 < 3e13 and 1e13 < f32 < 6e13
+
+
+def test_render_multi_bands_equal_single_device(engine):
+    """lyap_render_multi with three bands (all on device 0 here) gives the single-device bytes."""
+    kw = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=257, height=100, sequence="AABAB", iterations=120,
+              warmup=25, palette="aurora")
+    one = engine.render(L.make_params(**kw), want=("lambda", "norm", "rgba"))
+    multi = L.render_multi(L.make_params(**kw), [0, 0, 0])
+    assert np.array_equal(multi["lambda"].view(np.uint64), one["lambda"].view(np.uint64))
+    assert np.array_equal(multi["norm"].view(np.uint64), one["norm"].view(np.uint64))
+    assert np.array_equal(multi["rgba"], one["rgba"])
+    assert multi["stats"].executed_steps == one["stats"].executed_steps
+    assert (multi["stats"].lambda_min, multi["stats"].lambda_max) == (one["stats"].lambda_min, one["stats"].lambda_max)
+
+
+def test_render_multi_deadline_when_a_band_never_arrives(engine):
+    """A band whose worker never reaches the min/max exchange (ordinal -1 stands for it) ends the call with
+    LYAP_ERR_TIMEOUT after the host-side deadline; no GPU is made to hang for this."""
+    import time
+    p = L.make_params(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=64, height=32, sequence="AB", iterations=50,
+                      warmup=5)
+    t0 = time.time()
+    with pytest.raises(L.LyapError) as ei:
+        L.render_multi(p, [0, -1], timeout_seconds=0.5)
+    assert ei.value.status == 6 and "deadline" in str(ei.value)
+    assert 0.4 < time.time() - t0 < 10
+    # the library is still usable afterwards
+    ok = L.render_multi(p, [0, 0], want=("rgba",))
+    assert ok["rgba"].shape == (32, 64, 4)
+    with pytest.raises(L.LyapError):
+        L.render_multi(L.make_params(width=8, height=2, sequence="AB", iterations=5, warmup=1), [0, 0, 0])
+
+
+def test_cli_reproduces_the_page_call(engine, port, tmp_path):
+    """lyap_cli with no arguments is the page's call (800x800, [0,4]^2, 'AB', 1000 iterations, warm-up 100, cosmic)."""
+    import json
+    import os
+    import subprocess
+    from lyapunovfractalwasm_b200 import build
+    out = tmp_path / "frame.rgba"
+    r = subprocess.run([build.CLI, "--out", str(out)], check=True, capture_output=True, text=True)
+    info = json.loads(r.stdout.strip().splitlines()[-1])
+    assert (info["width"], info["height"], info["sequence"]) == (800, 800, "AB")
+    rgba = np.fromfile(out, dtype=np.uint8).reshape(800, 800, 4)
+    lam, steps = port.lambda_rows(0.0, 4.0, 0.0, 4.0, 800, 800, "AB", 1000, 100)
+    assert info["executed_steps"] == steps
+    assert np.array_equal(rgba, port.colorize(port.normalize(lam), 0))
+    ppm = tmp_path / "two.ppm"
+    subprocess.run([build.CLI, "--config", "1", "--gpus", "2", "--palette", "rainbow", "--out", str(ppm)], check=False)
+    if os.path.exists(ppm):   # needs two devices; on a one-GPU box the CLI reports the error instead
+        assert ppm.stat().st_size == 512 * 512 * 3 + len(b"P6\n512 512\n255\n")
