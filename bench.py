@@ -29,8 +29,9 @@ CFG2 = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=4096, height=4096,
             iterations=2000, warmup=200)
 # fp64 instructions per logistic step in the exact kernel's main path, counted from its source:
 #   warm-up step      3  (r*x, 1-x, product)
-#   accumulated step 14  (fma(-2,x,1), r*|.|, 8 for the log incl. its last addition, sum +=, r*x, 1-x, product)
-OPS_WARM, OPS_ACC = 3, 14
+#   accumulated step 13  (fma(-2,x,1), r*|.|, 7 for the log incl. its last addition, sum +=, r*x, 1-x, product)
+# The log's other two products, e*ln2hi and (e-1023)*ln2lo, come from a 4096-entry shared-memory table.
+OPS_WARM, OPS_ACC = 3, 13
 FAST_OPS = 4   # fast modes: 4 fused instructions per step on the fp64 / fp32 pipe
 
 

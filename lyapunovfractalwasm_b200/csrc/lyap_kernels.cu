@@ -7,6 +7,7 @@
 //
 // Build with -fmad=false: the exact kernels may only fuse where an fma is written out.
 #include <cfloat>
+#include <math_constants.h>
 #include <cstdint>
 #include <cstdlib>
 
@@ -34,13 +35,20 @@ __device__ const lyap_logtab_entry g_lyap_logtab[LYAP_LOG_BINS] = {LYAP_LOG_TABL
 // Steps run in chunks of up to 16 without per-step exit tests.  That is sound because leaving (0,1)
 // is permanent for x <- r x (1-x) with r > 0 (x >= 1 gives x <= 0 next, x <= 0 stays <= 0, NaN stays
 // NaN), so testing x after the chunk finds every exit, and the only other irregular event, a zero
-// derivative (x == 0.5 exactly, skipped and not counted by the reference, :71-74), shows up as a
-// zero exponent field, tracked with an integer min over the steps.  A chunk in which anything irregular
+// derivative (x == 0.5 exactly, skipped and not counted by the reference, :71-74), has exponent field 0,
+// for which the exponent table holds -inf: the running sum turns non-finite.  A chunk in which anything irregular
 // happened is rolled back and redone by `careful_chunk`, which follows the reference step by step.
 // ---------------------------------------------------------------------------------------------
 
 constexpr int kTabCopies = 8;
 constexpr size_t kTabSmemBytes = (size_t)LYAP_LOG_BINS * kTabCopies * sizeof(lyap_logtab_entry);  // 128 KB
+// Second shared table, indexed by the top 12 bits of the derivative (sign + exponent field e): {e*LN2HI (exact),
+// (e-1023)*LN2LO}.  It replaces an integer->double conversion and one fma per logarithm, and it carries the
+// irregular cases: entry 0 (zero or subnormal derivative) is -inf and entries >= 2047 (inf, NaN, sign bit) are NaN,
+// so such a step poisons the running sum and the chunk is redone step by step.
+constexpr int kExpEntries = 4096;
+constexpr size_t kExpSmemBytes = (size_t)kExpEntries * sizeof(double2);                              // 64 KB
+constexpr size_t kExactSmemBytes = kTabSmemBytes + kExpSmemBytes;
 
 __device__ __forceinline__ bool in_unit_interval(double x) { return x > 0.0 && x < 1.0; }
 
@@ -96,30 +104,30 @@ struct LogConsts {
 __constant__ LogConsts c_logk = {LYAP_LOG_C2, LYAP_LOG_C3, LYAP_LOG_C4, LYAP_LN2HI, LYAP_LN2LO, LYAP_KLO_BIAS};
 __constant__ int c_minus_2p20 = -(1 << 20);   // read as a constant-bank operand so the product below stays one multiply-add
 
-// lyap_log_core (lyap_math.h) for a positive normal d, written against the interleaved shared-memory
-// table: `tab_addr` is the shared-window byte address of this lane's copy of entry 0, entries are
-// kTabCopies*16 bytes apart.  Same operations in the same order as lyap_log_core, so same bits.
-__device__ __forceinline__ double log_fast(double d, unsigned tab_addr, unsigned& hw_out) {
+// lyap_log_core (lyap_math.h) for a positive normal d, written against the two shared-memory tables:
+// `tab_addr` is the shared-window byte address of this lane's copy of entry 0 of the mantissa table (entries are
+// kTabCopies*16 bytes apart), `exp_addr` that of the exponent table.  Same values in the same order as
+// lyap_log_core (e*LN2HI + lp and (e-1023)*LN2LO are tabulated instead of computed), so same bits.
+__device__ __forceinline__ double log_fast(double d, unsigned tab_addr, unsigned exp_addr) {
     const unsigned hw = (unsigned)__double2hiint(d);
-    hw_out = hw;
     const unsigned off = (hw >> 3) & (unsigned)((LYAP_LOG_BINS - 1) * kTabCopies * 16);   // bin index * 128 bytes
     double lp, invcb;
     asm("ld.shared.v2.f64 {%0, %1}, [%2];" : "=d"(lp), "=d"(invcb) : "r"(tab_addr + off));
-    // The shared copy holds invc with 0x3FF00000 added to its high word, so subtracting d's exponent field
+    const unsigned ke = hw >> 20;
+    double khi, klo;
+    asm("ld.shared.v2.f64 {%0, %1}, [%2];" : "=d"(khi), "=d"(klo) : "r"(exp_addr + ke * 16u));
+    // The mantissa table holds invc with 0x3FF00000 added to its high word, so subtracting d's exponent field
     // gives invc * 2^-(exponent of d): d * that == mantissa(d) * invc exactly (a power-of-two rescaling),
     // without assembling the mantissa as a separate double.
-    const int ke = (int)(hw >> 20);
     int invs_hi;
-    asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(invs_hi) : "r"(ke), "r"(c_minus_2p20), "r"(__double2hiint(invcb)));
+    asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(invs_hi) : "r"((int)ke), "r"(c_minus_2p20), "r"(__double2hiint(invcb)));
     const double invs = __hiloint2double(invs_hi, __double2loint(invcb));
-    const double kd = (double)ke;
     const double r = __fma_rn(d, invs, -1.0);
     double q = __fma_rn(r, c_logk.c4, c_logk.c3);
     q = __fma_rn(r, q, c_logk.c2);
     const double w = __fma_rn(r, q, 1.0);
-    const double klo = __fma_rn(kd, c_logk.ln2lo, c_logk.klo_bias);
     const double s = __fma_rn(r, w, klo);
-    const double hi = __fma_rn(kd, c_logk.ln2hi, lp);
+    const double hi = __dadd_rn(khi, lp);      // exact: both on the 2^-42 grid
     return __dadd_rn(hi, s);
 }
 
@@ -129,8 +137,8 @@ __device__ __forceinline__ double log_fast(double d, unsigned tab_addr, unsigned
 // so the scheduler has U*P log chains to interleave.  The sum is still accumulated in step order.
 // The warp-uniform parameter choice is a select (no branch, so the block stays one scheduling region).
 template <int P, bool ACC, bool HAS_C, int U>
-__device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P], const double (&rA)[P],
-                                           const double (&rB)[P], double rC, unsigned word, unsigned tab_addr) {
+__device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], const double (&rA)[P],
+                                           const double (&rB)[P], double rC, unsigned word, unsigned tab_addr, unsigned exp_addr) {
     double d[U][P];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
@@ -149,18 +157,14 @@ __device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], un
     }
     if (ACC) {
         double z[U][P];
-        unsigned hw[U][P];
 #pragma unroll
         for (int j = 0; j < U; ++j)
 #pragma unroll
-            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, hw[j][p]);
+            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, exp_addr);
 #pragma unroll
         for (int p = 0; p < P; ++p) {
 #pragma unroll
-            for (int j = 0; j < U; ++j) {
-                lyap[p] = __dadd_rn(lyap[p], z[j][p]);
-                hwmin[p] = min(hwmin[p], hw[j][p]);              // a zero derivative leaves hw < 2^20
-            }
+            for (int j = 0; j < U; ++j) lyap[p] = __dadd_rn(lyap[p], z[j][p]);
         }
     }
 }
@@ -168,8 +172,8 @@ __device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], un
 // U steps whose parameter choices are known at compile time (PAT: 2 bits per step, 0 = A, 1 = B, 2 = C):
 // no selects, no per-step branches; every operand is fixed.
 template <int P, bool ACC, int U, unsigned PAT>
-__device__ __forceinline__ void fixed_group(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P], const double (&rA)[P],
-                                            const double (&rB)[P], double rC, unsigned tab_addr) {
+__device__ __forceinline__ void fixed_group(double (&x)[P], double (&lyap)[P], const double (&rA)[P],
+                                            const double (&rB)[P], double rC, unsigned tab_addr, unsigned exp_addr) {
     double d[U][P];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
@@ -186,18 +190,14 @@ __device__ __forceinline__ void fixed_group(double (&x)[P], double (&lyap)[P], u
     }
     if (ACC) {
         double z[U][P];
-        unsigned hw[U][P];
 #pragma unroll
         for (int j = 0; j < U; ++j)
 #pragma unroll
-            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, hw[j][p]);
+            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, exp_addr);
 #pragma unroll
         for (int p = 0; p < P; ++p) {
 #pragma unroll
-            for (int j = 0; j < U; ++j) {
-                lyap[p] = __dadd_rn(lyap[p], z[j][p]);
-                hwmin[p] = min(hwmin[p], hw[j][p]);
-            }
+            for (int j = 0; j < U; ++j) lyap[p] = __dadd_rn(lyap[p], z[j][p]);
         }
     }
 }
@@ -211,13 +211,13 @@ __host__ __device__ constexpr unsigned spread_bits(unsigned m) {
 // warp-uniform multiway branch per U steps instead of a choice per step.
 //   !HAS_C: idx has one bit per step (0 = A, 1 = B), U is 2 or 4.   HAS_C: idx is the raw 2-bit codes, U is 2.
 template <int P, bool ACC, bool HAS_C, int U>
-__device__ __forceinline__ void dispatch_group(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P],
+__device__ __forceinline__ void dispatch_group(double (&x)[P], double (&lyap)[P],
                                                const double (&rA)[P], const double (&rB)[P], double rC, unsigned idx,
-                                               unsigned tab_addr) {
+                                               unsigned tab_addr, unsigned exp_addr) {
 #define LYAP_CASE_AB(N) \
-    case N: fixed_group<P, ACC, U, spread_bits(N)>(x, lyap, hwmin, rA, rB, rC, tab_addr); break;
+    case N: fixed_group<P, ACC, U, spread_bits(N)>(x, lyap, rA, rB, rC, tab_addr, exp_addr); break;
 #define LYAP_CASE_RAW(N) \
-    case N: fixed_group<P, ACC, U, N>(x, lyap, hwmin, rA, rB, rC, tab_addr); break;
+    case N: fixed_group<P, ACC, U, N>(x, lyap, rA, rB, rC, tab_addr, exp_addr); break;
     if (HAS_C) {
         static_assert(!HAS_C || U == 2, "three-parameter groups are two steps long");
         switch (idx) {
@@ -227,11 +227,11 @@ __device__ __forceinline__ void dispatch_group(double (&x)[P], double (&lyap)[P]
         }
     } else if (U == 2) {
         if (idx & 1u) {
-            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(3)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
-            else fixed_group<P, ACC, U, spread_bits(1)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
+            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(3)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+            else fixed_group<P, ACC, U, spread_bits(1)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
         } else {
-            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(2)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
-            else fixed_group<P, ACC, U, spread_bits(0)>(x, lyap, hwmin, rA, rB, rC, tab_addr);
+            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(2)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+            else fixed_group<P, ACC, U, spread_bits(0)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
         }
     } else {
         switch (idx) {
@@ -257,20 +257,20 @@ __device__ __forceinline__ unsigned compress_even_bits(unsigned w) {
 
 // n steps of selector word `word` (2 bits per step: 0 = A, 1 = B, 2 = C).
 template <int P, bool ACC, bool HAS_C, int UNROLL>
-__device__ __forceinline__ void fast_chunk(double (&x)[P], double (&lyap)[P], unsigned (&hwmin)[P], const double (&rA)[P],
-                                           const double (&rB)[P], double rC, unsigned word, int n, unsigned tab_addr) {
+__device__ __forceinline__ void fast_chunk(double (&x)[P], double (&lyap)[P], const double (&rA)[P],
+                                           const double (&rB)[P], double rC, unsigned word, int n, unsigned tab_addr, unsigned exp_addr) {
     if (n == kStepsPerWord) {
         constexpr int U = HAS_C ? 2 : UNROLL;
         unsigned pat = HAS_C ? word : compress_even_bits(word);
         constexpr int kBits = HAS_C ? 2 * U : U;
 #pragma unroll 1
         for (int h = 0; h < kStepsPerWord / U; ++h) {
-            dispatch_group<P, ACC, HAS_C, U>(x, lyap, hwmin, rA, rB, rC, pat & ((1u << kBits) - 1u), tab_addr);
+            dispatch_group<P, ACC, HAS_C, U>(x, lyap, rA, rB, rC, pat & ((1u << kBits) - 1u), tab_addr, exp_addr);
             pat >>= kBits;
         }
     } else {
 #pragma unroll 1
-        for (int j = 0; j < n; ++j, word >>= 2) fast_group<P, ACC, HAS_C, 1>(x, lyap, hwmin, rA, rB, rC, word, tab_addr);
+        for (int j = 0; j < n; ++j, word >>= 2) fast_group<P, ACC, HAS_C, 1>(x, lyap, rA, rB, rC, word, tab_addr, exp_addr);
     }
 }
 
@@ -288,6 +288,15 @@ k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64,
     __syncthreads();
     const lyap_logtab_entry* tab = tab_all + (threadIdx.x & (kTabCopies - 1));
     const unsigned tab_addr = (unsigned)__cvta_generic_to_shared(tab);
+    double2* exp_tab = reinterpret_cast<double2*>(smem_raw + kTabSmemBytes);
+    for (int e = threadIdx.x; e < kExpEntries; e += THREADS) {
+        double2 v;
+        if (e == 0) v = make_double2(-CUDART_INF, 0.0);                       // zero / subnormal derivative
+        else if (e >= 2047) v = make_double2(CUDART_NAN, 0.0);                // inf, NaN, or a set sign bit
+        else v = make_double2(__dmul_rn((double)e, LYAP_LN2HI), __fma_rn((double)e, LYAP_LN2LO, LYAP_KLO_BIAS));
+        exp_tab[e] = v;
+    }
+    const unsigned exp_addr = (unsigned)__cvta_generic_to_shared(exp_tab);
 
     unsigned long long my_steps = 0;
     const long long tile_px = (long long)THREADS * P;
@@ -336,19 +345,18 @@ k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64,
                 const unsigned word = a.sel[word0 + c];
                 const int n = min(kStepsPerWord, nsteps - c * kStepsPerWord);
                 double sx[P], sl[P];
-                unsigned hwmin[P];
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     sx[p] = x[p];
                     sl[p] = lyap[p];
-                    hwmin[p] = 0x7FF00000u;
                 }
-                if (acc) fast_chunk<P, true, HAS_C, UNROLL>(x, lyap, hwmin, rA, rB, rC, word, n, tab_addr);
-                else fast_chunk<P, false, HAS_C, UNROLL>(x, lyap, hwmin, rA, rB, rC, word, n, tab_addr);
+                if (acc) fast_chunk<P, true, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, tab_addr, exp_addr);
+                else fast_chunk<P, false, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, tab_addr, exp_addr);
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     if (done[p]) continue;
-                    const bool regular = !careful_only[p] && in_unit_interval(x[p]) && hwmin[p] >= 0x00100000u;
+                    // an irregular derivative (zero, subnormal, non-finite) has made the sum non-finite through the exponent table
+                    const bool regular = !careful_only[p] && in_unit_interval(x[p]) && isfinite(lyap[p]);
                     if (regular) {
                         if (acc) valid[p] += n;
                         my_steps += (unsigned long long)n;
@@ -412,13 +420,13 @@ static cudaError_t launch_exact_variant(const LambdaArgs& a, double* out64, floa
                                         int sm_count, cudaStream_t st) {
     auto kern = k_lambda_exact<P, THREADS, HAS_C, UNROLL>;
     // the attribute is per device and cheap to set; doing it on every launch keeps this thread- and device-safe
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTabSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kExactSmemBytes);
     if (e != cudaSuccess) return e;
     const long long tile_px = (long long)THREADS * P;
     const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) return cudaSuccess;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    kern<<<grid, THREADS, kTabSmemBytes, st>>>(a, out64, out32, steps);
+    kern<<<grid, THREADS, kExactSmemBytes, st>>>(a, out64, out32, steps);
     return cudaGetLastError();
 }
 
