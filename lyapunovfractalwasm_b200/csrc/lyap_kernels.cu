@@ -430,13 +430,36 @@ static cudaError_t launch_exact_variant(const LambdaArgs& a, double* out64, floa
     return cudaGetLastError();
 }
 
-static int exact_variant_from_env() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("LYAP_EXACT_VARIANT");   // tuning knob for experiments; default 0
-        v = e ? atoi(e) : 0;
+// Pixels per thread for a launch of n pixels.  Large frames: 3 (measured best on B200).  Small frames are
+// dominated by how many rounds of tiles the busiest SM runs, so the count that minimises rounds * pixels-per-thread
+// (weighted by each shape's measured per-pixel cost) is taken.  LYAP_EXACT_VARIANT=0..4 overrides (tuning knob).
+static int exact_pixels_per_thread(long long n_pixels, int sm_count, int* threads) {
+    static const int env = [] {
+        const char* e = getenv("LYAP_EXACT_VARIANT");
+        return e ? atoi(e) : -1;
+    }();
+    *threads = 512;
+    switch (env) {
+        case 0: return 3;
+        case 1: return 2;
+        case 3: return 4;
+        case 4: *threads = 1024; return 2;
+        default: break;
     }
-    return v;
+    const int cand[3] = {3, 2, 4};
+    const double cost[3] = {1.0, 1.035, 1.015};
+    int best = 3;
+    double best_t = 1e300;
+    for (int i = 0; i < 3; ++i) {
+        const long long tiles = (n_pixels + 512LL * cand[i] - 1) / (512LL * cand[i]);
+        const long long rounds = (tiles + sm_count - 1) / sm_count;
+        const double t = (double)rounds * cand[i] * cost[i];
+        if (t < best_t * 0.999) {
+            best_t = t;
+            best = cand[i];
+        }
+    }
+    return best;
 }
 
 cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
@@ -447,14 +470,12 @@ cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32
 #define LYAP_VARIANT(P, T, U)                                                                    \
     (has_c ? launch_exact_variant<P, T, true, U>(a, out64, out32, steps, sm_count, st)            \
            : launch_exact_variant<P, T, false, U>(a, out64, out32, steps, sm_count, st))
-    switch (exact_variant_from_env()) {
-        default:
-        case 0: return LYAP_VARIANT(3, 512, 2);   // measured best on B200 (4096^2 "AABAB")
-        case 1: return LYAP_VARIANT(2, 512, 2);
-        case 2: return LYAP_VARIANT(2, 512, 4);
-        case 3: return LYAP_VARIANT(4, 512, 2);
-        case 4: return LYAP_VARIANT(2, 1024, 2);
-    }
+    int threads = 512;
+    const int ppt = exact_pixels_per_thread(a.n_pixels, sm_count, &threads);
+    if (threads == 1024) return LYAP_VARIANT(2, 1024, 2);
+    if (ppt == 2) return LYAP_VARIANT(2, 512, 2);
+    if (ppt == 4) return LYAP_VARIANT(4, 512, 2);
+    return LYAP_VARIANT(3, 512, 2);
 #undef LYAP_VARIANT
 }
 
