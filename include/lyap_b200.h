@@ -185,6 +185,12 @@ int lyap_render_multi(const lyap_params* p, int32_t n_devices, const int32_t* de
 #define LYAP_NOALLOC_MAX_VALUES (1ull << 32)
 int lyap_minmax_device_noalloc(const double* d_values, uint64_t n, double* d_minmax, void* cuda_stream);
 
+/* No counterpart in the reference.  For a periodic sequence the exact lambda kernel may run as an instance compiled
+ * at run time for that sequence's A/B(/C) patterns (same source, same bits, no per-step choice left); environment
+ * LYAP_JIT=0 disables that, 2 compiles on first use instead of after about 2e10 steps of work with the sequence.
+ * Returns why the last attempt to build or use such an instance fell back to the precompiled kernel ("" if none did). */
+const char* lyap_jit_note(void);
+
 /* ---- measurement ---- */
 
 /* Issue-rate micro-benchmark of the fp64 pipe on the context's device: independent DFMA chains,

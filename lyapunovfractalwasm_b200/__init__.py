@@ -60,6 +60,7 @@ ABI = {
     "lyap_abi_version": (ctypes.c_int, []),
     "lyap_self_test": (ctypes.c_int, []),
     "lyap_last_error": (ctypes.c_char_p, []),
+    "lyap_jit_note": (ctypes.c_char_p, []),
     "lyap_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "lyap_params_default": (None, [ctypes.POINTER(LyapParams)]),
     "lyap_palette_from_name": (ctypes.c_int, [ctypes.c_char_p]),

@@ -168,6 +168,8 @@ int lyap_abi_version(void) { return LYAP_ABI_VERSION; }
 
 int lyap_self_test(void) { return 42; }
 
+const char* lyap_jit_note(void) { return lyap::jit_last_note(); }
+
 const char* lyap_last_error(void) { return g_last_error.c_str(); }
 
 const char* lyap_status_string(int s) {

@@ -4,24 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "lyap_args.h"
+
 namespace lyap {
-
-// Per-step parameter selectors, 2 bits per step (0 = A/column, 1 = B/row, 2 = C/scalar), 16 steps per
-// 32-bit word.  Warm-up steps start at word 0, accumulation steps at word `acc_word0`, each region in
-// its own words so both can be walked in whole 16-step chunks plus one partial chunk.
-constexpr int kStepsPerWord = 16;
-constexpr int kMaxSelWords = 896;  // 14336 steps through kernel parameters (kernel parameter space is 4 KB)
-
-struct LambdaArgs {
-    double min_x, min_y, dx, dy, c_value;
-    long long row_begin;   // global index of the first row of this launch
-    long long n_pixels;    // rows * width
-    int width;
-    int warmup, iterations;
-    int acc_word0;
-    int fast_ok_c;         // c_value is positive, finite and of ordinary magnitude (or unused)
-    unsigned int sel[kMaxSelWords];
-};
 
 struct LaunchInfo {
     int sm_count;
@@ -33,6 +18,13 @@ cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out3
                                  int sm_count, cudaStream_t st);
 cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                  int sm_count, cudaStream_t st);
+
+// run-time specialised instance of the exact kernel (lyap_jit.cu); *launched == false means "not used, launch the
+// precompiled kernel".  mode: 0 never, 1 once enough work with this sequence has been seen, 2 always.
+cudaError_t launch_lambda_exact_spec(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                     int sm_count, cudaStream_t st, int pixels_per_thread, size_t smem_bytes, int mode,
+                                     bool* launched);
+const char* jit_last_note();
 
 // scratch for the min/max reduction: 2*kMinmaxBlocks doubles + one unsigned ticket (zero before first use;
 // the kernel leaves it zero again)

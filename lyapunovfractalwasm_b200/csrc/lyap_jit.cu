@@ -1,0 +1,228 @@
+// lyap_jit.cu -- run-time specialisation of the exact lambda kernel for one sequence.
+//
+// The library's precompiled kernel picks, every two steps, the straight-line body that matches the next A/B(/C)
+// pattern (one warp-uniform multiway branch).  For a periodic sequence that choice is known in advance, so this
+// file compiles, once per (device, sequence patterns), an instance of the SAME kernel source
+// (lyap_exact_kernel.cuh, embedded as text at build time) in which a whole period is one straight-line block.
+// NVRTC does the compilation (found with dlopen: no link-time dependency); the driver entry points for loading and
+// launching come from cudaGetDriverEntryPoint.  Everything here is optional: if any step fails, the caller falls
+// back to the precompiled kernel, which computes the same bits.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "lyap_engine.h"
+#include "lyap_jit_source.inc"   // generated: kSrc_lyap_exact_kernel_cuh, kSrc_lyap_args_h, kSrc_lyap_math_h, kSrc_lyap_tables_h
+
+namespace lyap {
+
+namespace {
+
+struct Nvrtc {
+    void* lib = nullptr;
+    decltype(&nvrtcCreateProgram) create = nullptr;
+    decltype(&nvrtcCompileProgram) compile = nullptr;
+    decltype(&nvrtcGetCUBINSize) cubin_size = nullptr;
+    decltype(&nvrtcGetCUBIN) cubin = nullptr;
+    decltype(&nvrtcGetProgramLogSize) log_size = nullptr;
+    decltype(&nvrtcGetProgramLog) log = nullptr;
+    decltype(&nvrtcDestroyProgram) destroy = nullptr;
+    bool ok = false;
+};
+
+struct Driver {
+    CUresult (*module_load_data)(CUmodule*, const void*) = nullptr;
+    CUresult (*module_get_function)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*func_set_attribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+    CUresult (*launch_kernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                              void**, void**) = nullptr;
+    bool ok = false;
+};
+
+std::mutex g_mu;
+std::string g_note;   // last reason a specialised kernel could not be used
+
+Nvrtc& nvrtc() {
+    static Nvrtc n = [] {
+        Nvrtc r;
+        const char* env = getenv("LYAP_NVRTC_PATH");
+        const char* names[] = {env, "libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so"};
+        for (const char* nm : names) {
+            if (!nm || !*nm) continue;
+            r.lib = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+            if (r.lib) break;
+        }
+        if (!r.lib) return r;
+#define LYAP_SYM(field, name) r.field = reinterpret_cast<decltype(r.field)>(dlsym(r.lib, name))
+        LYAP_SYM(create, "nvrtcCreateProgram");
+        LYAP_SYM(compile, "nvrtcCompileProgram");
+        LYAP_SYM(cubin_size, "nvrtcGetCUBINSize");
+        LYAP_SYM(cubin, "nvrtcGetCUBIN");
+        LYAP_SYM(log_size, "nvrtcGetProgramLogSize");
+        LYAP_SYM(log, "nvrtcGetProgramLog");
+        LYAP_SYM(destroy, "nvrtcDestroyProgram");
+#undef LYAP_SYM
+        r.ok = r.create && r.compile && r.cubin_size && r.cubin && r.log_size && r.log && r.destroy;
+        return r;
+    }();
+    return n;
+}
+
+Driver& driver() {
+    static Driver d = [] {
+        Driver r;
+        auto get = [](const char* name, void** fn) {
+            cudaDriverEntryPointQueryResult st;
+            return cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &st) == cudaSuccess &&
+                   st == cudaDriverEntryPointSuccess && *fn;
+        };
+        r.ok = get("cuModuleLoadData", reinterpret_cast<void**>(&r.module_load_data)) &&
+               get("cuModuleGetFunction", reinterpret_cast<void**>(&r.module_get_function)) &&
+               get("cuFuncSetAttribute", reinterpret_cast<void**>(&r.func_set_attribute)) &&
+               get("cuLaunchKernel", reinterpret_cast<void**>(&r.launch_kernel));
+        return r;
+    }();
+    return d;
+}
+
+using Key = std::tuple<int, int, int, unsigned long long, unsigned long long>;   // device, P, KG, warm-up pats, acc pats
+
+struct Entry {
+    CUfunction fn = nullptr;
+    bool failed = false;
+    double work_seen = 0;   // nominal steps asked for so far with this key (decides when compiling pays off)
+};
+
+std::map<Key, Entry> g_cache;
+
+bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
+    Nvrtc& n = nvrtc();
+    Driver& d = driver();
+    if (!n.ok) { g_note = "NVRTC library not found"; return false; }
+    if (!d.ok) { g_note = "driver entry points not available"; return false; }
+    char o_p[64], o_kg[64], o_wu[96], o_acc[96];
+    snprintf(o_p, sizeof o_p, "-DLYAP_SPEC_P=%d", std::get<1>(key));
+    snprintf(o_kg, sizeof o_kg, "-DLYAP_SPEC_KG=%d", std::get<2>(key));
+    snprintf(o_wu, sizeof o_wu, "-DLYAP_SPEC_WU_PATS=0x%llxull", std::get<3>(key));
+    snprintf(o_acc, sizeof o_acc, "-DLYAP_SPEC_ACC_PATS=0x%llxull", std::get<4>(key));
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", "-DLYAP_SPEC_THREADS=512",
+                          o_p, o_kg, o_wu, o_acc};
+    const char* header_src[] = {kSrc_lyap_args_h, kSrc_lyap_math_h, kSrc_lyap_tables_h};
+    const char* header_names[] = {"lyap_args.h", "lyap_math.h", "lyap_tables.h"};
+    nvrtcProgram prog = nullptr;
+    if (n.create(&prog, kSrc_lyap_exact_kernel_cuh, "lyap_exact_kernel_spec.cu", 3, header_src, header_names) != NVRTC_SUCCESS) {
+        g_note = "nvrtcCreateProgram failed";
+        return false;
+    }
+    const nvrtcResult rc = n.compile(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);
+    if (rc != NVRTC_SUCCESS) {
+        size_t ls = 0;
+        n.log_size(prog, &ls);
+        std::string log(ls, '\0');
+        if (ls) n.log(prog, log.data());
+        g_note = "run-time compilation failed: " + log.substr(0, 600);
+        n.destroy(&prog);
+        return false;
+    }
+    size_t cs = 0;
+    std::vector<char> cubin;
+    if (n.cubin_size(prog, &cs) != NVRTC_SUCCESS || cs == 0) {
+        g_note = "no cubin produced";
+        n.destroy(&prog);
+        return false;
+    }
+    cubin.resize(cs);
+    n.cubin(prog, cubin.data());
+    n.destroy(&prog);
+    cudaFree(nullptr);   // make sure the primary context of the current device exists and is current
+    CUmodule mod = nullptr;
+    if (d.module_load_data(&mod, cubin.data()) != CUDA_SUCCESS) { g_note = "cuModuleLoadData failed"; return false; }
+    CUfunction fn = nullptr;
+    if (d.module_get_function(&fn, mod, "k_lambda_exact_spec") != CUDA_SUCCESS) { g_note = "kernel symbol not found"; return false; }
+    if (d.func_set_attribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem_bytes) != CUDA_SUCCESS) {
+        g_note = "cuFuncSetAttribute failed";
+        return false;
+    }
+    e->fn = fn;
+    return true;
+}
+
+}  // namespace
+
+const char* jit_last_note() { return g_note.c_str(); }
+
+// Finds the group-pattern period of both regions of `a`.  Returns KG (1..16) and the two pattern words, or 0.
+int sequence_group_period(const LambdaArgs& a, unsigned long long* wu_pats, unsigned long long* acc_pats) {
+    auto code = [&](int word0, int i) { return (a.sel[word0 + i / kStepsPerWord] >> (2 * (i % kStepsPerWord))) & 3u; };
+    for (int kg = 1; kg <= 16; ++kg) {
+        const int bs = 2 * kg;
+        bool ok = true;
+        for (int i = bs; i < a.warmup && ok; ++i) ok = code(0, i) == code(0, i - bs);
+        for (int i = bs; i < a.iterations && ok; ++i) ok = code(a.acc_word0, i) == code(a.acc_word0, i - bs);
+        if (!ok) continue;
+        unsigned long long wu = 0, acc = 0;
+        for (int i = 0; i < bs; ++i) {
+            if (i < a.warmup) wu |= (unsigned long long)code(0, i) << (2 * i);
+            if (i < a.iterations) acc |= (unsigned long long)code(a.acc_word0, i) << (2 * i);
+        }
+        *wu_pats = wu;
+        *acc_pats = acc;
+        return kg;
+    }
+    return 0;
+}
+
+// Launches the specialised instance when there is one (or when compiling one now is worth it).
+// mode: 0 never, 1 when the work seen for this sequence passes a threshold, 2 always.
+// *launched tells whether a kernel was enqueued; false means "use the precompiled kernel".
+cudaError_t launch_lambda_exact_spec(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                     int sm_count, cudaStream_t st, int pixels_per_thread, size_t smem_bytes, int mode,
+                                     bool* launched) {
+    *launched = false;
+    if (mode <= 0) return cudaSuccess;
+    unsigned long long wu = 0, acc = 0;
+    const int kg = sequence_group_period(a, &wu, &acc);
+    if (kg == 0) return cudaSuccess;
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return ce;
+    const Key key{dev, pixels_per_thread, kg, wu, acc};
+    CUfunction fn = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        Entry& e = g_cache[key];
+        e.work_seen += (double)a.n_pixels * ((double)a.warmup + a.iterations);
+        if (!e.fn && !e.failed && (mode >= 2 || e.work_seen >= 2e10)) {
+            if (!compile_entry(key, &e, smem_bytes)) e.failed = true;
+        }
+        fn = e.fn;
+    }
+    if (!fn) return cudaSuccess;
+    const long long tile_px = 512LL * pixels_per_thread;
+    const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
+    if (tiles <= 0) { *launched = true; return cudaSuccess; }
+    const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+    void* params[] = {const_cast<LambdaArgs*>(&a), &out64, &out32, &steps};
+    const CUresult r = driver().launch_kernel(fn, grid, 1, 1, 512, 1, 1, (unsigned)smem_bytes, (CUstream)st, params, nullptr);
+    if (r != CUDA_SUCCESS) {
+        std::lock_guard<std::mutex> lk(g_mu);
+        g_note = "cuLaunchKernel of the specialised kernel failed";
+        g_cache[key].fn = nullptr;
+        g_cache[key].failed = true;
+        return cudaSuccess;   // not launched: the caller uses the precompiled kernel
+    }
+    *launched = true;
+    return cudaSuccess;
+}
+
+}  // namespace lyap

@@ -15,8 +15,16 @@
 //   lyap_exp : < 1 ulp;  lyap_pow(t, 1.2 | 1.5) : < 1.5 ulp;  lyap_sin, lyap_cos : < 2 ulp for |x| <= 30
 #pragma once
 
+#if defined(__CUDACC_RTC__)
+// run-time compilation has no host headers: the few fixed-width names used below
+typedef unsigned int uint32_t;
+typedef unsigned long long uint64_t;
+typedef long long int64_t;
+typedef unsigned long long uintptr_t;
+#else
 #include <stdint.h>
 #include <string.h>
+#endif
 #include "lyap_tables.h"
 
 #if defined(__CUDACC__)
