@@ -333,7 +333,8 @@ def main():
         peak = fp32_peak if mode == L.MODE_FAST_FP32 else fp64_peak
         out_bytes = rows_all * width * 8
         roofline = {
-            "kernel": {L.MODE_EXACT: "k_lambda_exact", L.MODE_FAST_FP64: "k_lambda_fast<double>",
+            "kernel": {L.MODE_EXACT: "k_lambda_exact_spec (k_lambda_exact compiled at run time for this sequence; LYAP_JIT=0: precompiled)"
+                       if os.environ.get("LYAP_JIT", "1") != "0" else "k_lambda_exact", L.MODE_FAST_FP64: "k_lambda_fast<double>",
                        L.MODE_FAST_FP32: "k_lambda_fast<float>"}[mode],
             "bound": "fp32_pipe" if mode == L.MODE_FAST_FP32 else "fp64_pipe",
             "achieved": achieved / 1e12, "peak": peak / 1e12, "unit": "T thread-instr/s", "frac": achieved / peak,
@@ -342,8 +343,8 @@ def main():
             "instr_per_step": {"warmup": OPS_WARM, "accumulated": OPS_ACC} if mode == L.MODE_EXACT else FAST_OPS,
             "ms_per_launch": ms_lambda,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch on the 4096x4096 frame (ncu, profiles/):
-            # 2.0 MB read + 76.8 MB written; less than the 134 MB of stores because the tail is still in L2 at kernel end
-            "traffic": 78.9e6 * rows_all / 4096 if mode == L.MODE_EXACT else None,
+            # 2.3 MB read + 76.9 MB written; less than the 134 MB of stores because the tail is still in L2 at kernel end
+            "traffic": 79.2e6 * rows_all / 4096 if mode == L.MODE_EXACT else None,
             "hbm": {"algorithmic_bytes_per_launch": out_bytes, "store_gbs": out_bytes / (ms_lambda * 1e-3) / 1e9,
                     "peak_gbs": hbm_peak, "peak_source": "MEASURED_PEAKS.json (measured)" if hbm_peak else "absent"},
         }
