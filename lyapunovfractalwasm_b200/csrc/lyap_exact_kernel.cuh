@@ -372,21 +372,27 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
 #pragma unroll
                     for (int p = 0; p < P; ++p) all_done = all_done && done[p];
                     if (__all_sync(0xFFFFFFFFu, all_done)) break;
-                    const bool whole = s + CS <= nsteps;
-                    const int n = whole ? CS : nsteps - s;
+                    const int left = nsteps - s;
+                    const int n = left >= CS ? CS : (left >= BS ? left / BS * BS : left);
                     double sx[P], sl[P];
 #pragma unroll
                     for (int p = 0; p < P; ++p) {
                         sx[p] = x[p];
                         sl[p] = lyap[p];
                     }
-                    if (whole) {
+                    if (left >= CS) {             // CB whole periods, straight-line
 #pragma unroll
                         for (int b = 0; b < CB; ++b) {
                             if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
                             else period_block<P, false, KG, WU_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
                         }
-                    } else {
+                    } else if (left >= BS) {      // the last few whole periods
+#pragma unroll 1
+                        for (int b = 0; b < n / BS; ++b) {
+                            if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+                            else period_block<P, false, KG, WU_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+                        }
+                    } else {                      // less than one period: one step at a time
 #pragma unroll 1
                         for (int j = s; j < nsteps; ++j) {
                             const unsigned code = (sel[j / kStepsPerWord] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;

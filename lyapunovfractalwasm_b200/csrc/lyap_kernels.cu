@@ -77,7 +77,7 @@ cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32
     const int ppt = exact_pixels_per_thread(a.n_pixels, sm_count, &threads);
     // a periodic sequence can run an instance of this kernel compiled for its patterns (LYAP_JIT=0 turns that off,
     // 2 compiles at once instead of after some work has been seen)
-    if (threads == 512) {
+    if (threads == 512 && ppt <= 3) {   // with 4 pixels per thread the specialised instance measured slower
         const char* je = getenv("LYAP_JIT");
         const int jit_mode = je ? atoi(je) : 1;
         bool launched = false;
