@@ -42,7 +42,7 @@ def engine():
     eng.close()
 
 
-# the five benchmark configurations (BASELINE.json), as make_params keywords
+# the benchmark configurations 1-4, as make_params keywords (5 is config5_frame below)
 CONFIGS = {
     1: dict(min_x=2.0, max_x=4.0, min_y=2.0, max_y=4.0, width=512, height=512, sequence="AB",
             iterations=1000, warmup=100),
