@@ -137,6 +137,13 @@ int lyap_normalize_device(lyap_ctx* ctx, const double* d_values, uint64_t n, con
 int lyap_colorize_device(lyap_ctx* ctx, const double* d_norm, int32_t width, int64_t rows,
                          int32_t rows_above, int32_t rows_below, int32_t palette, uint8_t* d_rgba);
 
+/* applyGlow (web/fractal_renderer.js:313-334) on an RGBA8 frame in place: three self-draws with 'screen' compositing
+ * (blur 6 px at alpha 0.3, blur 2 px at 0.4, unfiltered at 0.1).  The reference leaves the arithmetic to the
+ * browser's compositor; this is the engine's own reading of the Canvas / CSS filter rules (Gaussian of the given
+ * standard deviation truncated at 3 sigma, transparent outside the canvas, 8-bit rounding after each draw).
+ * d_scratch: width*height*24 bytes of device memory. */
+int lyap_glow_device(lyap_ctx* ctx, uint8_t* d_rgba, int32_t width, int32_t height, void* d_scratch);
+
 /* ---- host-pointer entry points (blocking) ---- */
 
 /* computeFractal (src/lyapunov_fractal.hpp:27): out_lambda holds rows*width doubles. */
@@ -148,6 +155,9 @@ int lyap_normalize_data(lyap_ctx* ctx, const double* values, uint64_t n, double*
 /* renderFractal up to putImageData (web/fractal_renderer.js:177-200) for a whole frame. */
 int lyap_colorize(lyap_ctx* ctx, const double* norm, int32_t width, int32_t height, int32_t palette,
                   uint8_t* out_rgba);
+
+/* applyGlow for a frame in host memory (see lyap_glow_device); rgba_in and rgba_out may be the same buffer. */
+int lyap_glow(lyap_ctx* ctx, const uint8_t* rgba_in, int32_t width, int32_t height, uint8_t* rgba_out);
 
 /* The binding's whole call order (src/wasm_bindings.cpp:109-125: parse, computeFractal,
  * normalizeData) followed by the page's colour stage, on the whole frame.  Any output may be NULL.

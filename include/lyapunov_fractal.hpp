@@ -103,4 +103,13 @@ inline std::vector<std::uint8_t> renderRGBA(const std::vector<double>& normalize
     return rgba;
 }
 
+// The page's glow pass (web/fractal_renderer.js:313-334) on an RGBA8 frame, the engine's reading of it.
+inline std::vector<std::uint8_t> applyGlow(const std::vector<std::uint8_t>& rgba, int width, int height) {
+    if (width < 1 || height < 1 || rgba.size() != static_cast<std::size_t>(width) * static_cast<std::size_t>(height) * 4)
+        throw std::runtime_error("applyGlow: size mismatch");
+    std::vector<std::uint8_t> out(rgba.size());
+    detail::check(lyap_glow(detail::context(), rgba.data(), width, height, out.data()), "applyGlow");
+    return out;
+}
+
 }  // namespace lyapunov

@@ -83,6 +83,8 @@ ABI = {
     "lyap_compute_fractal": (ctypes.c_int, [_P, ctypes.POINTER(LyapParams), _P, _P]),
     "lyap_normalize_data": (ctypes.c_int, [_P, _P, ctypes.c_uint64, _P]),
     "lyap_colorize": (ctypes.c_int, [_P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _P]),
+    "lyap_glow_device": (ctypes.c_int, [_P, _P, ctypes.c_int32, ctypes.c_int32, _P]),
+    "lyap_glow": (ctypes.c_int, [_P, _P, ctypes.c_int32, ctypes.c_int32, _P]),
     "lyap_render": (ctypes.c_int, [_P, ctypes.POINTER(LyapParams), _P, _P, _P, _P, _P,
                                    ctypes.POINTER(RenderStats)]),
     "lyap_render_multi": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), _P, _P,
@@ -250,6 +252,13 @@ class Engine:
         out = np.empty((h, w, 4), dtype=np.uint8)
         pal = PALETTES.index(palette) if isinstance(palette, str) else palette
         _check(self.lib.lyap_colorize(self.ctx, norm.ctypes.data, w, h, pal, out.ctypes.data))
+        return out
+
+    def glow(self, rgba):
+        rgba = np.ascontiguousarray(rgba, dtype=np.uint8)
+        h, w, _ = rgba.shape
+        out = np.empty_like(rgba)
+        _check(self.lib.lyap_glow(self.ctx, rgba.ctypes.data, w, h, out.ctypes.data))
         return out
 
     # ---- device-pointer API ----

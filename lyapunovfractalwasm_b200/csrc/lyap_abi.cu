@@ -372,6 +372,15 @@ int lyap_colorize_device(lyap_ctx* c, const double* d_norm, int32_t width, int64
     return LYAP_OK;
 }
 
+int lyap_glow_device(lyap_ctx* c, uint8_t* d_rgba, int32_t width, int32_t height, void* d_scratch) {
+    if (int r = check_ctx(c)) return r;
+    if (width < 1 || height < 1) return fail(LYAP_ERR_INVALID, "bad dimensions");
+    if (!d_rgba || !d_scratch) return fail(LYAP_ERR_INVALID, "null pointer");
+    cudaError_t e = lyap::launch_glow(d_rgba, width, height, static_cast<double*>(d_scratch), c->stream);
+    if (e != cudaSuccess) return fail_cuda(e, "glow launch");
+    return LYAP_OK;
+}
+
 // ---- host-pointer entry points ----
 
 int lyap_render(lyap_ctx* c, const lyap_params* p, double* out_lambda, float* out_lambda32, double* out_norm,
@@ -671,6 +680,22 @@ extern "C" int lyap_render_multi(const lyap_params* p, int32_t n_devices, const 
 }
 
 extern "C" {
+
+int lyap_glow(lyap_ctx* c, const uint8_t* rgba_in, int32_t width, int32_t height, uint8_t* rgba_out) {
+    if (int r = check_ctx(c)) return r;
+    if (width < 1 || height < 1) return fail(LYAP_ERR_INVALID, "bad dimensions");
+    if (!rgba_in || !rgba_out) return fail(LYAP_ERR_INVALID, "null pointer");
+    const size_t n = (size_t)width * height;
+    if (int r = ensure(c, c->rgba, n * 4)) return r;
+    if (int r = ensure(c, c->norm, n * 24)) return r;   // the blur's scratch shares the normalised-frame buffer
+    cudaStream_t st = c->stream;
+    CU(cudaMemcpyAsync(c->rgba.p, rgba_in, n * 4, cudaMemcpyHostToDevice, st));
+    cudaError_t e = lyap::launch_glow(static_cast<uint8_t*>(c->rgba.p), width, height, static_cast<double*>(c->norm.p), st);
+    if (e != cudaSuccess) return fail_cuda(e, "glow launch");
+    CU(cudaMemcpyAsync(rgba_out, c->rgba.p, n * 4, cudaMemcpyDeviceToHost, st));
+    CU(cudaStreamSynchronize(st));
+    return LYAP_OK;
+}
 
 // ---- measurement ----
 

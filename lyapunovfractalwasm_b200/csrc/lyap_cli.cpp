@@ -29,13 +29,14 @@ struct Options {
     bool has_c = false;
     double c = 0.0;
     int gpus = 1, frame = 0;
+    bool glow = false;
 };
 
 [[noreturn]] void usage(const char* why) {
     std::cerr << "lyap_cli: " << why << "\n"
               << "usage: lyap_cli [--config 1..5 [--frame K]] [--width W --height H --min-x .. --max-x .. --min-y .. --max-y ..]\n"
               << "                [--sequence S] [--iterations N] [--warmup N] [--c V] [--palette NAME]\n"
-              << "                [--mode exact|fast64|fast32] [--gpus N] [--out file.ppm|.rgba|.f64]\n";
+              << "                [--mode exact|fast64|fast32] [--gpus N] [--glow] [--out file.ppm|.rgba|.f64]\n";
     std::exit(2);
 }
 
@@ -98,6 +99,7 @@ int main(int argc, char** argv) {
         else if (a == "--mode") o.mode = std::string(next());
         else if (a == "--gpus") o.gpus = to_int(next());
         else if (a == "--out") o.out = std::string(next());
+        else if (a == "--glow") o.glow = true;
         else usage("unknown option");
     }
 
@@ -132,6 +134,13 @@ int main(int argc, char** argv) {
         std::vector<int32_t> devs(o.gpus);
         for (int i = 0; i < o.gpus; ++i) devs[i] = i;
         status = lyap_render_multi(&p, o.gpus, devs.data(), nullptr, want_f64 ? norm.data() : nullptr, rgba.data(), 0.0, &st);
+    }
+    if (status == LYAP_OK && o.glow) {   // the page's last step (web/fractal_renderer.js:203)
+        lyap_ctx* ctx = nullptr;
+        if ((status = lyap_create(&ctx, 0)) == LYAP_OK) {
+            status = lyap_glow(ctx, rgba.data(), o.width, o.height, rgba.data());
+            lyap_destroy(ctx);
+        }
     }
     const double wall_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     if (status != LYAP_OK) {

@@ -36,6 +36,9 @@ cudaError_t launch_normalize(const double* v, unsigned long long n, const double
 cudaError_t launch_colorize(const double* norm, int width, long long rows, int rows_above, int rows_below,
                             int palette, unsigned char* rgba, cudaStream_t st);
 
+// glow on an RGBA8 canvas in place; scratch holds width*height*3 doubles
+cudaError_t launch_glow(unsigned char* canvas, int width, int height, double* scratch, cudaStream_t st);
+
 // issue-rate micro-benchmarks; return thread-level instructions executed per launch
 cudaError_t launch_fp64_peak(double* sink, int sm_count, int iters, unsigned long long* instr, cudaStream_t st);
 cudaError_t launch_fp32_peak(float* sink, int sm_count, int iters, unsigned long long* instr, cudaStream_t st);

@@ -421,6 +421,114 @@ cudaError_t launch_colorize(const double* norm, int width, long long rows, int r
 }
 
 // ---------------------------------------------------------------------------------------------
+// Glow (web/fractal_renderer.js:313-334): the canvas drawn onto itself three times with 'screen' compositing,
+// blur(6px) at alpha 0.3, blur(2px) at alpha 0.4, unfiltered at alpha 0.1.  The browser's compositor defines
+// the exact arithmetic in the reference; these kernels implement this project's reading of the Canvas / CSS
+// rules (stated in full beside oracle_glow in the CPU checker): Gaussian truncated at ceil(3 sigma),
+// transparent black outside, opaque backdrop, out = Cb + alpha * Sp * (1 - Cb), 8-bit rounding per draw.
+// ---------------------------------------------------------------------------------------------
+constexpr int kGlowMaxRadius = 18;
+struct GlowArgs {
+    double w[2 * kGlowMaxRadius + 1];
+    double alpha;
+    int radius;   // 0: no filter
+};
+constexpr int kGlowThreads = 256;
+
+__global__ void __launch_bounds__(kGlowThreads)
+k_glow_blur_rows(const __grid_constant__ GlowArgs g, const unsigned char* __restrict__ canvas, int width, long long n,
+                 double* __restrict__ tmp) {
+    __shared__ double unit[256];
+    unit[threadIdx.x] = __ddiv_rn((double)threadIdx.x, 255.0);
+    __syncthreads();
+    const long long nthreads = (long long)gridDim.x * kGlowThreads;
+    for (long long i = (long long)blockIdx.x * kGlowThreads + threadIdx.x; i < n; i += nthreads) {
+        const int x = (int)(i % width);
+        double s0 = 0.0, s1 = 0.0, s2 = 0.0;
+        for (int k = -g.radius; k <= g.radius; ++k) {
+            const int xx = x + k;
+            if (xx >= 0 && xx < width) {
+                const uchar4 c = *reinterpret_cast<const uchar4*>(canvas + (i + k) * 4);
+                const double wk = g.w[k + g.radius];
+                s0 = __dadd_rn(s0, __dmul_rn(wk, unit[c.x]));
+                s1 = __dadd_rn(s1, __dmul_rn(wk, unit[c.y]));
+                s2 = __dadd_rn(s2, __dmul_rn(wk, unit[c.z]));
+            }
+        }
+        tmp[i * 3] = s0;
+        tmp[i * 3 + 1] = s1;
+        tmp[i * 3 + 2] = s2;
+    }
+}
+
+__device__ __forceinline__ unsigned char glow_mix(double cb, double sp, double alpha) {
+    const double out = __dadd_rn(cb, __dmul_rn(__dmul_rn(alpha, sp), __dsub_rn(1.0, cb)));
+    const double q = floor(__dadd_rn(__dmul_rn(out, 255.0), 0.5));
+    return (unsigned char)(q < 0.0 ? 0.0 : (q > 255.0 ? 255.0 : q));
+}
+
+__global__ void __launch_bounds__(kGlowThreads)
+k_glow_blur_cols_mix(const __grid_constant__ GlowArgs g, unsigned char* __restrict__ canvas, int width, int height,
+                     long long n, const double* __restrict__ tmp) {
+    __shared__ double unit[256];
+    unit[threadIdx.x] = __ddiv_rn((double)threadIdx.x, 255.0);
+    __syncthreads();
+    const long long nthreads = (long long)gridDim.x * kGlowThreads;
+    for (long long i = (long long)blockIdx.x * kGlowThreads + threadIdx.x; i < n; i += nthreads) {
+        const uchar4 cb = *reinterpret_cast<const uchar4*>(canvas + i * 4);
+        double s0, s1, s2;
+        if (g.radius > 0) {
+            const int y = (int)(i / width);
+            s0 = s1 = s2 = 0.0;
+            for (int k = -g.radius; k <= g.radius; ++k) {
+                const int yy = y + k;
+                if (yy >= 0 && yy < height) {
+                    const double* t = tmp + (i + (long long)k * width) * 3;
+                    const double wk = g.w[k + g.radius];
+                    s0 = __dadd_rn(s0, __dmul_rn(wk, t[0]));
+                    s1 = __dadd_rn(s1, __dmul_rn(wk, t[1]));
+                    s2 = __dadd_rn(s2, __dmul_rn(wk, t[2]));
+                }
+            }
+        } else {
+            s0 = unit[cb.x];
+            s1 = unit[cb.y];
+            s2 = unit[cb.z];
+        }
+        uchar4 o;
+        o.x = glow_mix(unit[cb.x], s0, g.alpha);
+        o.y = glow_mix(unit[cb.y], s1, g.alpha);
+        o.z = glow_mix(unit[cb.z], s2, g.alpha);
+        o.w = cb.w;
+        *reinterpret_cast<uchar4*>(canvas + i * 4) = o;
+    }
+}
+
+cudaError_t launch_glow(unsigned char* canvas, int width, int height, double* scratch, cudaStream_t st) {
+    const long long n = (long long)width * height;
+    if (n <= 0) return cudaSuccess;
+    const long long want = (n + kGlowThreads - 1) / kGlowThreads;
+    const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+    const double sigmas[3] = {6.0, 2.0, 0.0}, alphas[3] = {0.3, 0.4, 0.1};
+    for (int pass = 0; pass < 3; ++pass) {
+        GlowArgs g{};
+        g.alpha = alphas[pass];
+        g.radius = (int)ceil(3.0 * sigmas[pass]);
+        if (g.radius > 0) {
+            double sum = 0.0;
+            for (int k = -g.radius; k <= g.radius; ++k) {
+                g.w[k + g.radius] = lyap_exp(-(double)(k * k) / (2.0 * sigmas[pass] * sigmas[pass]));
+                sum += g.w[k + g.radius];
+            }
+            for (int k = 0; k <= 2 * g.radius; ++k) g.w[k] /= sum;
+            k_glow_blur_rows<<<grid, kGlowThreads, 0, st>>>(g, canvas, width, n, scratch);
+        }
+        k_glow_blur_cols_mix<<<grid, kGlowThreads, 0, st>>>(g, canvas, width, height, n, scratch);
+    }
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // Pipe issue-rate micro-benchmarks: 8 independent FMA chains per thread, nothing else in the loop.
 // ---------------------------------------------------------------------------------------------
 constexpr int kPeakThreads = 512;

@@ -12,6 +12,7 @@
 //   oracle_box3             web/fractal_renderer.js:283-311  applyPostProcessing
 //   oracle_palette          web/fractal_renderer.js:207-281  getColorFunction (+ hslToRgb :26-47)
 //   oracle_colorize         web/fractal_renderer.js:177-198  renderFractal up to the ImageData store
+//   oracle_glow             web/fractal_renderer.js:313-334  applyGlow (browser-defined; this project's reading)
 //
 // Differences from the reference, on purpose:
 //   * rows are addressed by their GLOBAL index (r_y = min_y + dy*y_global with the global dy), so
@@ -264,6 +265,75 @@ void oracle_colorize(const double* norm, int width, int height, int palette, uin
         oracle_palette(boxed[i], palette, rgba + 4 * i);
         rgba[4 * i + 3] = 255;
     }
+}
+
+// Glow: three self-draws of the canvas with 'screen' compositing (web/fractal_renderer.js:313-334):
+// blur(6px) at alpha 0.3, blur(2px) at alpha 0.4, no filter at alpha 0.1.  The browser's compositor defines the
+// exact arithmetic there; this is the engine's own reading of the Canvas / CSS filter rules, the same one the CUDA
+// kernels follow: Gaussian of standard deviation sigma truncated at ceil(3 sigma) and normalised, transparent black
+// outside the canvas, premultiplied source, opaque backdrop, so per channel
+//     out = Cb + alpha * Sp * (1 - Cb),   Sp = blurred premultiplied source,
+// and the canvas is rounded to 8 bits after each draw.
+static void glow_weights(double sigma, std::vector<double>& w) {
+    const int R = (int)std::ceil(3.0 * sigma);
+    w.assign(2 * R + 1, 0.0);
+    double sum = 0.0;
+    for (int k = -R; k <= R; ++k) {
+        w[k + R] = lyap_exp(-(double)(k * k) / (2.0 * sigma * sigma));
+        sum += w[k + R];
+    }
+    for (double& v : w) v /= sum;
+}
+
+static void glow_pass(std::vector<uint8_t>& canvas, int width, int height, double sigma, double alpha) {
+    const size_t n = (size_t)width * height;
+    std::vector<double> sp(n * 3);
+    if (sigma > 0.0) {
+        std::vector<double> w;
+        glow_weights(sigma, w);
+        const int R = (int)(w.size() / 2);
+        std::vector<double> tmp(n * 3);
+#pragma omp parallel for
+        for (int y = 0; y < height; ++y)
+            for (int x = 0; x < width; ++x)
+                for (int c = 0; c < 3; ++c) {
+                    double s = 0.0;
+                    for (int k = -R; k <= R; ++k) {
+                        const int xx = x + k;
+                        if (xx >= 0 && xx < width) s += w[k + R] * (canvas[((size_t)y * width + xx) * 4 + c] / 255.0);
+                    }
+                    tmp[((size_t)y * width + x) * 3 + c] = s;
+                }
+#pragma omp parallel for
+        for (int y = 0; y < height; ++y)
+            for (int x = 0; x < width; ++x)
+                for (int c = 0; c < 3; ++c) {
+                    double s = 0.0;
+                    for (int k = -R; k <= R; ++k) {
+                        const int yy = y + k;
+                        if (yy >= 0 && yy < height) s += w[k + R] * tmp[((size_t)yy * width + x) * 3 + c];
+                    }
+                    sp[((size_t)y * width + x) * 3 + c] = s;
+                }
+    } else {
+        for (size_t i = 0; i < n; ++i)
+            for (int c = 0; c < 3; ++c) sp[i * 3 + c] = canvas[i * 4 + c] / 255.0;
+    }
+    for (size_t i = 0; i < n; ++i)
+        for (int c = 0; c < 3; ++c) {
+            const double cb = canvas[i * 4 + c] / 255.0;
+            const double out = cb + alpha * sp[i * 3 + c] * (1.0 - cb);
+            double q = std::floor(out * 255.0 + 0.5);
+            canvas[i * 4 + c] = (uint8_t)(q < 0.0 ? 0.0 : (q > 255.0 ? 255.0 : q));
+        }
+}
+
+void oracle_glow(const uint8_t* rgba_in, int width, int height, uint8_t* rgba_out) {
+    std::vector<uint8_t> canvas(rgba_in, rgba_in + (size_t)width * height * 4);
+    glow_pass(canvas, width, height, 6.0, 0.3);
+    glow_pass(canvas, width, height, 2.0, 0.4);
+    glow_pass(canvas, width, height, 0.0, 0.1);
+    std::memcpy(rgba_out, canvas.data(), canvas.size());
 }
 
 int oracle_abi_version(void) { return 1; }

@@ -43,6 +43,7 @@ class Port:
         L.oracle_box3.argtypes = [c_double_p, ctypes.c_int, ctypes.c_int, c_double_p]
         L.oracle_colorize.argtypes = [c_double_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, c_u8_p]
         L.oracle_palette.argtypes = [ctypes.c_double, ctypes.c_int, c_u8_p]
+        L.oracle_glow.argtypes = [c_u8_p, ctypes.c_int, ctypes.c_int, c_u8_p]
 
     def hash64(self, arr):
         a = np.ascontiguousarray(arr)
@@ -88,6 +89,13 @@ class Port:
         h, w = norm.shape
         out = np.empty((h, w, 4), dtype=np.uint8)
         self.lib.oracle_colorize(_dp(norm), w, h, palette, out.ctypes.data_as(c_u8_p))
+        return out
+
+    def glow(self, rgba):
+        rgba = np.ascontiguousarray(rgba, dtype=np.uint8)
+        h, w, _ = rgba.shape
+        out = np.empty_like(rgba)
+        self.lib.oracle_glow(rgba.ctypes.data_as(c_u8_p), w, h, out.ctypes.data_as(c_u8_p))
         return out
 
     def palette(self, t, palette):

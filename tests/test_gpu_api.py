@@ -177,3 +177,17 @@ def test_cli_reproduces_the_page_call(engine, port, tmp_path):
     subprocess.run([build.CLI, "--config", "1", "--gpus", "2", "--palette", "rainbow", "--out", str(ppm)], check=False)
     if os.path.exists(ppm):   # needs two devices; on a one-GPU box the CLI reports the error instead
         assert ppm.stat().st_size == 512 * 512 * 3 + len(b"P6\n512 512\n255\n")
+
+
+def test_glow_matches_the_cpu_restatement(engine, port):
+    """applyGlow as the engine defines it (the browser defines it in the reference: parity unpinned there)."""
+    kw = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=301, height=123, sequence="AB", iterations=150, warmup=30)
+    rgba = engine.render(L.make_params(**kw), want=("rgba",))["rgba"]
+    got = engine.glow(rgba)
+    want = port.glow(rgba)
+    assert np.array_equal(got, want)
+    assert np.all(got[..., 3] == 255) and np.all(got[..., :3].astype(int) >= rgba[..., :3].astype(int))   # 'screen' only brightens
+    tiny = np.zeros((3, 5, 4), dtype=np.uint8)
+    tiny[..., 3] = 255
+    tiny[1, 2, :3] = 200
+    assert np.array_equal(engine.glow(tiny), port.glow(tiny))
