@@ -19,11 +19,12 @@ cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out3
 cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                  int sm_count, cudaStream_t st);
 
-// run-time specialised instance of the exact kernel (lyap_jit.cu); *launched == false means "not used, launch the
-// precompiled kernel".  mode: 0 never, 1 once enough work with this sequence has been seen, 2 always.
-cudaError_t launch_lambda_exact_spec(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
-                                     int sm_count, cudaStream_t st, int pixels_per_thread, size_t smem_bytes, int mode,
-                                     bool* launched);
+// run-time specialised instance of a lambda kernel (lyap_jit.cu); kind: 0 exact, 1 fast fp64, 2 fast fp32.
+// *launched == false means "not used, launch the precompiled kernel".  mode: 0 never, 1 once enough work with this
+// sequence has been seen, 2 always.
+cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps, int sm_count,
+                               cudaStream_t st, int kind, int pixels_per_thread, int threads, size_t smem_bytes, int mode,
+                               bool* launched);
 const char* jit_last_note();
 
 // scratch for the min/max reduction: 2*kMinmaxBlocks doubles + one unsigned ticket (zero before first use;

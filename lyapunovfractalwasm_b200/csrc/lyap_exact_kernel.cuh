@@ -513,7 +513,7 @@ k_lambda_exact(const __grid_constant__ LambdaArgs a, double* __restrict__ out64,
     lambda_exact_body<P, THREADS, HAS_C, UNROLL, 0, 0ull, 0ull>(a, out64, out32, steps_out);
 }
 
-#if defined(LYAP_SPEC_KG)
+#if defined(LYAP_SPEC_EXACT)
 // The specialised instance; LYAP_SPEC_* are given on the run-time compiler's command line.
 extern "C" __global__ void __launch_bounds__(LYAP_SPEC_THREADS, 1)
 k_lambda_exact_spec(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,

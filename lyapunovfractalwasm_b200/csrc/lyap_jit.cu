@@ -22,7 +22,7 @@
 #include <vector>
 
 #include "lyap_engine.h"
-#include "lyap_jit_source.inc"   // generated: kSrc_lyap_exact_kernel_cuh, kSrc_lyap_args_h, kSrc_lyap_math_h, kSrc_lyap_tables_h
+#include "lyap_jit_source.inc"   // generated: kSrc_lyap_exact_kernel_cuh, kSrc_lyap_kernels_fast_cuh, kSrc_lyap_args_h, ...
 
 namespace lyap {
 
@@ -95,7 +95,7 @@ Driver& driver() {
     return d;
 }
 
-using Key = std::tuple<int, int, int, unsigned long long, unsigned long long>;   // device, P, KG, warm-up pats, acc pats
+using Key = std::tuple<int, int, int, unsigned long long, unsigned long long, int, int>;   // device, P, KG, warm-up pats, acc pats, kind, threads
 
 struct Entry {
     CUfunction fn = nullptr;
@@ -110,17 +110,23 @@ bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
     Driver& d = driver();
     if (!n.ok) { g_note = "NVRTC library not found"; return false; }
     if (!d.ok) { g_note = "driver entry points not available"; return false; }
-    char o_p[64], o_kg[64], o_wu[96], o_acc[96];
+    char o_p[64], o_kg[64], o_wu[96], o_acc[96], o_thr[64];
+    const int kind = std::get<5>(key);
+    snprintf(o_thr, sizeof o_thr, "-DLYAP_SPEC_THREADS=%d", std::get<6>(key));
+    // the exact instance is compiled when LYAP_SPEC_KG is defined without a fast type; a fast one when the type is given
+    const char* o_kind = kind == 0 ? "-DLYAP_SPEC_EXACT=1" : (kind == 1 ? "-DLYAP_SPEC_FAST_TYPE=double" : "-DLYAP_SPEC_FAST_TYPE=float");
     snprintf(o_p, sizeof o_p, "-DLYAP_SPEC_P=%d", std::get<1>(key));
     snprintf(o_kg, sizeof o_kg, "-DLYAP_SPEC_KG=%d", std::get<2>(key));
     snprintf(o_wu, sizeof o_wu, "-DLYAP_SPEC_WU_PATS=0x%llxull", std::get<3>(key));
     snprintf(o_acc, sizeof o_acc, "-DLYAP_SPEC_ACC_PATS=0x%llxull", std::get<4>(key));
-    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", "-DLYAP_SPEC_THREADS=512",
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", o_thr, o_kind,
                           o_p, o_kg, o_wu, o_acc};
-    const char* header_src[] = {kSrc_lyap_args_h, kSrc_lyap_math_h, kSrc_lyap_tables_h};
-    const char* header_names[] = {"lyap_args.h", "lyap_math.h", "lyap_tables.h"};
+    const char* header_src[] = {kSrc_lyap_exact_kernel_cuh, kSrc_lyap_kernels_fast_cuh, kSrc_lyap_args_h, kSrc_lyap_math_h,
+                                kSrc_lyap_tables_h};
+    const char* header_names[] = {"lyap_exact_kernel.cuh", "lyap_kernels_fast.cuh", "lyap_args.h", "lyap_math.h", "lyap_tables.h"};
+    static const char kMain[] = "#include \"lyap_exact_kernel.cuh\"\n#include \"lyap_kernels_fast.cuh\"\n";
     nvrtcProgram prog = nullptr;
-    if (n.create(&prog, kSrc_lyap_exact_kernel_cuh, "lyap_exact_kernel_spec.cu", 3, header_src, header_names) != NVRTC_SUCCESS) {
+    if (n.create(&prog, kMain, "lyap_spec.cu", 5, header_src, header_names) != NVRTC_SUCCESS) {
         g_note = "nvrtcCreateProgram failed";
         return false;
     }
@@ -148,8 +154,8 @@ bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
     CUmodule mod = nullptr;
     if (d.module_load_data(&mod, cubin.data()) != CUDA_SUCCESS) { g_note = "cuModuleLoadData failed"; return false; }
     CUfunction fn = nullptr;
-    if (d.module_get_function(&fn, mod, "k_lambda_exact_spec") != CUDA_SUCCESS) { g_note = "kernel symbol not found"; return false; }
-    if (d.func_set_attribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem_bytes) != CUDA_SUCCESS) {
+    if (d.module_get_function(&fn, mod, kind == 0 ? "k_lambda_exact_spec" : "k_lambda_fast_spec") != CUDA_SUCCESS) { g_note = "kernel symbol not found"; return false; }
+    if (smem_bytes && d.func_set_attribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem_bytes) != CUDA_SUCCESS) {
         g_note = "cuFuncSetAttribute failed";
         return false;
     }
@@ -185,9 +191,9 @@ int sequence_group_period(const LambdaArgs& a, unsigned long long* wu_pats, unsi
 // Launches the specialised instance when there is one (or when compiling one now is worth it).
 // mode: 0 never, 1 when the work seen for this sequence passes a threshold, 2 always.
 // *launched tells whether a kernel was enqueued; false means "use the precompiled kernel".
-cudaError_t launch_lambda_exact_spec(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
-                                     int sm_count, cudaStream_t st, int pixels_per_thread, size_t smem_bytes, int mode,
-                                     bool* launched) {
+cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps, int sm_count,
+                               cudaStream_t st, int kind, int pixels_per_thread, int threads, size_t smem_bytes, int mode,
+                               bool* launched) {
     *launched = false;
     if (mode <= 0) return cudaSuccess;
     unsigned long long wu = 0, acc = 0;
@@ -196,7 +202,7 @@ cudaError_t launch_lambda_exact_spec(const LambdaArgs& a, double* out64, float* 
     int dev = 0;
     cudaError_t ce = cudaGetDevice(&dev);
     if (ce != cudaSuccess) return ce;
-    const Key key{dev, pixels_per_thread, kg, wu, acc};
+    const Key key{dev, pixels_per_thread, kg, wu, acc, kind, threads};
     CUfunction fn = nullptr;
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -208,12 +214,13 @@ cudaError_t launch_lambda_exact_spec(const LambdaArgs& a, double* out64, float* 
         fn = e.fn;
     }
     if (!fn) return cudaSuccess;
-    const long long tile_px = 512LL * pixels_per_thread;
+    const long long tile_px = (long long)threads * pixels_per_thread;
     const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) { *launched = true; return cudaSuccess; }
-    const unsigned grid = (unsigned)(tiles < sm_count ? tiles : sm_count);
+    const long long cap = kind == 0 ? sm_count : 4LL * sm_count;   // the exact kernel's shared tables allow one CTA per SM
+    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
     void* params[] = {const_cast<LambdaArgs*>(&a), &out64, &out32, &steps};
-    const CUresult r = driver().launch_kernel(fn, grid, 1, 1, 512, 1, 1, (unsigned)smem_bytes, (CUstream)st, params, nullptr);
+    const CUresult r = driver().launch_kernel(fn, grid, 1, 1, (unsigned)threads, 1, 1, (unsigned)smem_bytes, (CUstream)st, params, nullptr);
     if (r != CUDA_SUCCESS) {
         std::lock_guard<std::mutex> lk(g_mu);
         g_note = "cuLaunchKernel of the specialised kernel failed";

@@ -81,8 +81,8 @@ cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32
         const char* je = getenv("LYAP_JIT");
         const int jit_mode = je ? atoi(je) : 1;
         bool launched = false;
-        const cudaError_t e = launch_lambda_exact_spec(a, out64, out32, steps, sm_count, st, ppt, kExactSmemBytes, jit_mode,
-                                                       &launched);
+        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, 0, ppt, 512, kExactSmemBytes, jit_mode,
+                                                 &launched);
         if (e != cudaSuccess) return e;
         if (launched) return cudaSuccess;
     }

@@ -1,4 +1,5 @@
-// lyap_kernels_fast.cuh -- fast-mode lambda kernels (included by lyap_kernels.cu).
+// lyap_kernels_fast.cuh -- fast-mode lambda kernels (included by lyap_kernels.cu after lyap_exact_kernel.cuh, and, as
+// text, by the run-time specialiser).
 //
 // Same pixel mapping, sequence handling, sentinel and early-exit rules as the exact kernel, but the
 // arithmetic is rearranged for speed and is NOT bit-compatible with the reference:
@@ -98,6 +99,61 @@ __device__ __forceinline__ void fast_mode_steps(T (&x)[P], T (&prod)[P], const T
     }
 }
 
+// fast_careful_chunk for steps [first, first + n) of a region whose selector words start at `sel`.
+template <typename T, bool ACC>
+__device__ __noinline__ bool fast_careful_steps(FastPixel<T>* ps, T rA, T rB, T rC, const unsigned* sel, int first, int n,
+                                                unsigned long long* steps) {
+    bool dead = false;
+    int j = first;
+    const int end = first + n;
+    while (j < end && !dead) {
+        const int in_word = j & (kStepsPerWord - 1);
+        const int m = min(kStepsPerWord - in_word, end - j);
+        dead = fast_careful_chunk<T, ACC>(ps, rA, rB, rC, sel[j / kStepsPerWord] >> (2 * in_word), m, steps);
+        j += m;
+    }
+    return dead;
+}
+
+// Moves the exponent of every pixel's running product into its integer sum and notes the extreme exponent fields.
+template <typename T, int P>
+__device__ __forceinline__ void strip_products(T (&prod)[P], int (&esum)[P], int (&emin)[P], int (&emax)[P]) {
+    using F = FastTraits<T>;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+        const int e = F::strip(prod[p]);
+        emin[p] = min(emin[p], e);
+        emax[p] = max(emax[p], e);
+        esum[p] += e - F::kBias;
+    }
+}
+
+// Run-time specialisation (see lyap_jit.cu): NG two-step groups whose patterns are compile-time constants
+// (PATS: 4 bits per group, repeating every KG groups), as one straight-line block; the products are stripped
+// every kRenorm steps and after the last group.
+template <typename T, int P, bool ACC, int KG, unsigned long long PATS, int NG, int GI = 0>
+__device__ __forceinline__ void fast_fixed_groups(T (&x)[P], T (&prod)[P], int (&esum)[P], int (&emin)[P], int (&emax)[P],
+                                                  const T (&rA)[P], const T (&rB)[P], const T (&rC)[P]) {
+    using F = FastTraits<T>;
+    if constexpr (GI < NG) {
+        constexpr unsigned pat = (unsigned)((PATS >> (4 * (GI % KG))) & 15ull);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            constexpr unsigned code0 = pat & 3u, code1 = (pat >> 2) & 3u;
+            const unsigned code = j == 0 ? code0 : code1;
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                const T r = code == 0 ? rA[p] : (code == 1 ? rB[p] : rC[p]);
+                const T t = F::mul(r, x[p]);
+                if (ACC) prod[p] = F::mul(prod[p], F::abs_(F::fma_((T)-2, t, r)));
+                x[p] = F::fma_(-t, x[p], t);
+            }
+        }
+        if (ACC && ((2 * (GI + 1)) % F::kRenorm == 0 || GI == NG - 1)) strip_products<T, P>(prod, esum, emin, emax);
+        fast_fixed_groups<T, P, ACC, KG, PATS, NG, GI + 1>(x, prod, esum, emin, emax, rA, rB, rC);
+    }
+}
+
 template <typename T>
 __device__ __forceinline__ bool ordinary_param_t(T r);
 template <>
@@ -105,10 +161,10 @@ __device__ __forceinline__ bool ordinary_param_t<double>(double r) { return r > 
 template <>
 __device__ __forceinline__ bool ordinary_param_t<float>(float r) { return r > 0x1p-20f && r < 0x1p5f; }
 
-template <typename T, int P, int THREADS>
-__global__ void __launch_bounds__(THREADS)
-k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,
-              unsigned long long* __restrict__ steps_out) {
+// Body shared by the precompiled kernel (KG == 0) and a run-time specialised instance (KG > 0).
+template <typename T, int P, int THREADS, int KG, unsigned long long WU_PATS, unsigned long long ACC_PATS>
+__device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __restrict__ out64, float* __restrict__ out32,
+                                                 unsigned long long* __restrict__ steps_out) {
     using F = FastTraits<T>;
     unsigned long long my_steps = 0;
     const long long tile_px = (long long)THREADS * P;
@@ -155,6 +211,81 @@ k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, 
             const bool acc = region == 1;
             const int nsteps = acc ? a.iterations : a.warmup;
             const int word0 = acc ? a.acc_word0 : 0;
+            if constexpr (KG > 0) {
+                constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, CS = CB * BS;
+                const unsigned* sel = a.sel + word0;
+                int s = 0;
+                while (s < nsteps) {
+                    bool all_done = true;
+#pragma unroll
+                    for (int p = 0; p < P; ++p) all_done = all_done && done[p];
+                    if (__all_sync(0xFFFFFFFFu, all_done)) break;
+                    const int left = nsteps - s;
+                    const int n = left >= CS ? CS : (left >= BS ? left / BS * BS : left);
+                    T sx[P], sp[P];
+                    int se[P], emin[P], emax[P];
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        sx[p] = x[p];
+                        sp[p] = prod[p];
+                        se[p] = esum[p];
+                        emin[p] = F::kExpMax;
+                        emax[p] = 0;
+                    }
+                    if (left >= CS) {
+                        if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                        else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                    } else if (left >= BS) {
+#pragma unroll 1
+                        for (int b = 0; b < n / BS; ++b) {
+                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                            else fast_fixed_groups<T, P, false, KG, WU_PATS, KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int j = s; j < nsteps; ++j) {
+                            const unsigned code = (sel[j / kStepsPerWord] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
+                            if (acc) {
+                                if (code == 0) fast_mode_steps<T, P, true>(x, prod, rA);
+                                else if (code == 1) fast_mode_steps<T, P, true>(x, prod, rB);
+                                else fast_mode_steps<T, P, true>(x, prod, rC);
+                                if ((j - s + 1) % F::kRenorm == 0 || j == nsteps - 1) strip_products<T, P>(prod, esum, emin, emax);
+                            } else {
+                                if (code == 0) fast_mode_steps<T, P, false>(x, prod, rA);
+                                else if (code == 1) fast_mode_steps<T, P, false>(x, prod, rB);
+                                else fast_mode_steps<T, P, false>(x, prod, rC);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        if (done[p]) continue;
+                        const bool regular = !careful_only[p] && (x[p] > (T)0 && x[p] < (T)1) &&
+                                             (!acc || (emin[p] != 0 && emax[p] != F::kExpMax));
+                        if (regular) {
+                            if (acc) valid[p] += n;
+                            my_steps += (unsigned long long)n;
+                        } else {
+                            esum[p] = se[p];
+                            prod[p] = sp[p];
+                            FastPixel<T> ps{sx[p], extra[p], valid[p]};
+                            const bool dead =
+                                acc ? fast_careful_steps<T, true>(&ps, rA[p], rB[p], rC[p], sel, s, n, &my_steps)
+                                    : fast_careful_steps<T, false>(&ps, rA[p], rB[p], rC[p], sel, s, n, &my_steps);
+                            x[p] = ps.x;
+                            extra[p] = ps.extra;
+                            valid[p] = ps.valid;
+                            if (dead) {
+                                done[p] = true;
+                                lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
+                                x[p] = (T)0.25;
+                            }
+                        }
+                    }
+                    s += n;
+                }
+                continue;
+            }
             const int nchunks = (nsteps + kStepsPerWord - 1) / kStepsPerWord;
             for (int c = 0; c < nchunks; ++c) {
                 bool all_done = true;
@@ -254,9 +385,36 @@ k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, 
 
 constexpr int kFastThreads = 256;
 
+template <typename T, int P, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,
+              unsigned long long* __restrict__ steps_out) {
+    lambda_fast_body<T, P, THREADS, 0, 0ull, 0ull>(a, out64, out32, steps_out);
+}
+
+#if defined(LYAP_SPEC_FAST_TYPE)
+// The specialised instance; LYAP_SPEC_* are given on the run-time compiler's command line.
+extern "C" __global__ void __launch_bounds__(LYAP_SPEC_THREADS)
+k_lambda_fast_spec(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,
+                   unsigned long long* __restrict__ steps_out) {
+    lambda_fast_body<LYAP_SPEC_FAST_TYPE, LYAP_SPEC_P, LYAP_SPEC_THREADS, LYAP_SPEC_KG, LYAP_SPEC_WU_PATS, LYAP_SPEC_ACC_PATS>(
+        a, out64, out32, steps_out);
+}
+#endif
+
+#if !defined(__CUDACC_RTC__)
 template <typename T, int P>
 static cudaError_t launch_lambda_fast_t(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                         int sm_count, cudaStream_t st) {
+    {   // a periodic sequence can run an instance compiled for its patterns (same switch as the exact kernel)
+        const char* je = getenv("LYAP_JIT");
+        bool launched = false;
+        // measured best shapes for the specialised instances: fp64 4 pixels/thread, fp32 2 pixels/thread, 512 threads
+        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, sizeof(T) == 8 ? 1 : 2,
+                                                 sizeof(T) == 8 ? 4 : 2, 512, 0, je ? atoi(je) : 1, &launched);
+        if (e != cudaSuccess) return e;
+        if (launched) return cudaSuccess;
+    }
     const long long tile_px = (long long)kFastThreads * P;
     const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) return cudaSuccess;
@@ -280,5 +438,6 @@ cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out3
                                  int sm_count, cudaStream_t st) {
     return launch_lambda_fast_t<float, 4>(a, out64, out32, steps, sm_count, st);
 }
+#endif
 
 }  // namespace lyap
