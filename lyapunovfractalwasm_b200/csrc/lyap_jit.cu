@@ -104,14 +104,17 @@ struct Entry {
 };
 
 std::map<Key, Entry> g_cache;
+// compiled code does not depend on the device ordinal: one compilation serves every GPU of the process
+using CodeKey = std::tuple<int, int, unsigned long long, unsigned long long, int, int>;   // Key without the device
+std::map<CodeKey, std::vector<char>> g_cubins;
 
-bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
+// NVRTC: source text + pattern macros -> cubin for sm_100a.
+bool compile_cubin(const Key& key, std::vector<char>* out) {
     Nvrtc& n = nvrtc();
-    Driver& d = driver();
-    if (!n.ok) { g_note = "NVRTC library not found"; return false; }
-    if (!d.ok) { g_note = "driver entry points not available"; return false; }
-    char o_p[64], o_kg[64], o_wu[96], o_acc[96], o_thr[64];
     const int kind = std::get<5>(key);
+    std::vector<char>& cubin = *out;
+    if (!n.ok) { g_note = "NVRTC library not found"; return false; }
+    char o_p[64], o_kg[64], o_wu[96], o_acc[96], o_thr[64];
     snprintf(o_thr, sizeof o_thr, "-DLYAP_SPEC_THREADS=%d", std::get<6>(key));
     // the exact instance is compiled when LYAP_SPEC_KG is defined without a fast type; a fast one when the type is given
     const char* o_kind = kind == 0 ? "-DLYAP_SPEC_EXACT=1" : (kind == 1 ? "-DLYAP_SPEC_FAST_TYPE=double" : "-DLYAP_SPEC_FAST_TYPE=float");
@@ -141,7 +144,6 @@ bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
         return false;
     }
     size_t cs = 0;
-    std::vector<char> cubin;
     if (n.cubin_size(prog, &cs) != NVRTC_SUCCESS || cs == 0) {
         g_note = "no cubin produced";
         n.destroy(&prog);
@@ -150,6 +152,20 @@ bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
     cubin.resize(cs);
     n.cubin(prog, cubin.data());
     n.destroy(&prog);
+    return true;
+}
+
+// Loads the (cached) cubin into the current device's context and looks the kernel up.
+bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
+    Driver& d = driver();
+    if (!d.ok) { g_note = "driver entry points not available"; return false; }
+    const int kind = std::get<5>(key);
+    const CodeKey ck{std::get<1>(key), std::get<2>(key), std::get<3>(key), std::get<4>(key), kind, std::get<6>(key)};
+    std::vector<char>& cubin = g_cubins[ck];
+    if (cubin.empty() && !compile_cubin(key, &cubin)) {
+        cubin.clear();
+        return false;
+    }
     cudaFree(nullptr);   // make sure the primary context of the current device exists and is current
     CUmodule mod = nullptr;
     if (d.module_load_data(&mod, cubin.data()) != CUDA_SUCCESS) { g_note = "cuModuleLoadData failed"; return false; }
