@@ -589,20 +589,30 @@ void multi_worker(MultiShared& sh, const lyap_params& base, int device, long lon
     double* d_mm = static_cast<double*>(d_small);
     uint64_t* d_steps = reinterpret_cast<uint64_t*>(d_mm + 2);
     uint64_t zero = 0;
-    lyap_params p = base;
-    p.row_begin = b0 - above;
-    p.row_end = b1 + below;
     double* own = static_cast<double*>(d_lam) + (size_t)above * W;
     st = lyap_copy_to_device(c, d_steps, &zero, 8);
-    if (st == LYAP_OK) st = lyap_lambda_device(c, &p, static_cast<double*>(d_lam), nullptr, d_steps);
+    {   // the band's own rows (counted), then the halo rows (same kernel, not counted)
+        lyap_params p = base;
+        p.row_begin = b0;
+        p.row_end = b1;
+        if (st == LYAP_OK) st = lyap_lambda_device(c, &p, own, nullptr, d_steps);
+        if (st == LYAP_OK && above) {
+            p.row_begin = b0 - 1;
+            p.row_end = b0;
+            st = lyap_lambda_device(c, &p, static_cast<double*>(d_lam), nullptr, nullptr);
+        }
+        if (st == LYAP_OK && below) {
+            p.row_begin = b1;
+            p.row_end = b1 + 1;
+            st = lyap_lambda_device(c, &p, own + (size_t)rows_own * W, nullptr, nullptr);
+        }
+    }
     if (st == LYAP_OK) st = lyap_minmax_device(c, own, (uint64_t)rows_own * W, d_mm);
     double mm[2];
     uint64_t steps = 0;
     if (st == LYAP_OK) st = lyap_copy_to_host(c, mm, d_mm, 16);
     if (st == LYAP_OK) st = lyap_copy_to_host(c, &steps, d_steps, 8);
     if (st != LYAP_OK) return bail(st);
-    // halo rows were computed too; count only the band's own share of the steps
-    steps = steps / (uint64_t)rows_all * (uint64_t)rows_own + steps % (uint64_t)rows_all * (uint64_t)rows_own / (uint64_t)rows_all;
     {   // the one exchange: min of mins, max of maxes, with a deadline
         std::unique_lock<std::mutex> lk(sh.mu);
         sh.lo = sh.have ? std::fmin(sh.lo, mm[0]) : mm[0];
@@ -674,7 +684,7 @@ extern "C" int lyap_render_multi(const lyap_params* p, int32_t n_devices, const 
         stats->lambda_min = sh.lo;
         stats->lambda_max = sh.hi;
         stats->ms_total_device = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
-        stats->kernel_launches = 4 * n_devices;
+        stats->kernel_launches = 6 * n_devices - 2;   // per band: lambda for own rows + up to two halo rows, min/max, normalise, colour
     }
     return LYAP_OK;
 }
