@@ -201,6 +201,14 @@ int lyap_minmax_device_noalloc(const double* d_values, uint64_t n, double* d_min
  * Returns why the last attempt to build or use such an instance fell back to the precompiled kernel ("" if none did). */
 const char* lyap_jit_note(void);
 
+/* No counterpart in the reference (host only, needs no GPU).  Writes to *code which parameter step `step` of the
+ * warm-up (region 0) or of the accumulation (region 1) uses under `params` -- 0 = column parameter ('A'),
+ * 1 = row parameter, 2 = c_value -- read back from the packed selector table the kernels are given, i.e. what
+ * sequence[(region ? warmup + step : step) % len] selects (src/lyapunov_fractal.hpp:37).  A region too long to store
+ * whole is stored as one period of the sequence in whole 16-step words and walked cyclically, so any warmup and
+ * iterations are accepted while 2 * len / gcd(len, 16) <= 896; longer sequences are limited to 14336 steps. */
+int lyap_selector_code(const lyap_params* params, int region, int64_t step, int* code);
+
 /* ---- measurement ---- */
 
 /* Issue-rate micro-benchmark of the fp64 pipe on the context's device: independent DFMA chains,

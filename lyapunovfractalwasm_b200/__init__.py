@@ -61,6 +61,7 @@ ABI = {
     "lyap_self_test": (ctypes.c_int, []),
     "lyap_last_error": (ctypes.c_char_p, []),
     "lyap_jit_note": (ctypes.c_char_p, []),
+    "lyap_selector_code": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.c_int, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)]),
     "lyap_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "lyap_params_default": (None, [ctypes.POINTER(LyapParams)]),
     "lyap_palette_from_name": (ctypes.c_int, [ctypes.c_char_p]),
@@ -135,6 +136,13 @@ def make_params(min_x=0.0, max_x=4.0, min_y=0.0, max_y=4.0, width=800, height=60
     p.c_value = 0.0 if c is None else c
     p.row_begin, p.row_end = row_begin, row_end
     return p
+
+
+def selector_code(params, region, step):
+    """lyap_selector_code: the parameter (0 = A, 1 = B, 2 = C) the kernels use at `step` of warm-up (0) / accumulation (1)."""
+    code = ctypes.c_int(-1)
+    _check(load_library().lyap_selector_code(ctypes.byref(params), region, step, ctypes.byref(code)))
+    return code.value
 
 
 NOALLOC_MAX_VALUES = 1 << 32

@@ -3,6 +3,7 @@
 // Host-side orchestration only: parameter checks, the sequence-to-selector packing
 // (reference src/lyapunov_fractal.hpp:34-38), buffer management, launches, copies, timing.
 // There is deliberately no CPU implementation behind these entry points.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -10,6 +11,7 @@
 #include <condition_variable>
 #include <mutex>
 #include <new>
+#include <numeric>
 #include <thread>
 #include <string>
 #include <vector>
@@ -99,11 +101,16 @@ int build_args(const lyap_params* p, lyap::LambdaArgs* a, Geometry* g) {
     if (rb == 0 && re == 0) re = p->height;
     if (rb < 0 || re > p->height || rb >= re) return fail(LYAP_ERR_INVALID, "row range must satisfy 0 <= begin < end <= height");
 
-    const int wu_words = (p->warmup + lyap::kStepsPerWord - 1) / lyap::kStepsPerWord;
-    const int acc_words = (p->iterations + lyap::kStepsPerWord - 1) / lyap::kStepsPerWord;
+    // A region is stored whole when it fits; otherwise as one period of the sequence in whole words
+    // (lcm(len, 16) steps = len / gcd(len, 16) words), which the kernels walk round and round.
+    const long long period_words = seq_len / std::gcd(seq_len, (long long)lyap::kStepsPerWord);
+    const long long wu_need = ((long long)p->warmup + lyap::kStepsPerWord - 1) / lyap::kStepsPerWord;
+    const long long acc_need = ((long long)p->iterations + lyap::kStepsPerWord - 1) / lyap::kStepsPerWord;
+    const long long wu_words = std::min(wu_need, period_words), acc_words = std::min(acc_need, period_words);
     if (wu_words + acc_words > lyap::kMaxSelWords)
         return fail(LYAP_ERR_TOO_LARGE, "warmup + iterations beyond " +
-                                            std::to_string(lyap::kMaxSelWords * lyap::kStepsPerWord) + " steps");
+                                            std::to_string(lyap::kMaxSelWords * lyap::kStepsPerWord) +
+                                            " steps with a sequence too long to store by its period");
 
     std::memset(a, 0, sizeof(*a));
     a->min_x = p->min_x;
@@ -116,7 +123,9 @@ int build_args(const lyap_params* p, lyap::LambdaArgs* a, Geometry* g) {
     a->width = p->width;
     a->warmup = p->warmup;
     a->iterations = p->iterations;
-    a->acc_word0 = wu_words;
+    a->acc_word0 = (int)wu_words;
+    a->wu_wrap = (int)std::max(1LL, wu_words);
+    a->acc_wrap = (int)std::max(1LL, acc_words);
     const bool use_c = p->c_enabled != 0;
     bool seq_has_c = false;
     // step i uses sequence[i % len]; 'A' -> column parameter, anything else -> row parameter (:37),
@@ -130,8 +139,10 @@ int build_args(const lyap_params* p, lyap::LambdaArgs* a, Geometry* g) {
         }
         return 1u;
     };
-    for (int i = 0; i < p->warmup; ++i) a->sel[i / 16] |= code(i) << (2 * (i % 16));
-    for (int i = 0; i < p->iterations; ++i)
+    const long long wu_stored = std::min<long long>(p->warmup, wu_words * lyap::kStepsPerWord);
+    const long long acc_stored = std::min<long long>(p->iterations, acc_words * lyap::kStepsPerWord);
+    for (long long i = 0; i < wu_stored; ++i) a->sel[i / 16] |= code(i) << (2 * (i % 16));
+    for (long long i = 0; i < acc_stored; ++i)
         a->sel[wu_words + i / 16] |= code((long long)p->warmup + i) << (2 * (i % 16));
     const double c = p->c_value;
     a->fast_ok_c = (!seq_has_c || (c > 0x1p-20 && c < 0x1p20)) ? 1 : 0;
@@ -169,6 +180,18 @@ int lyap_abi_version(void) { return LYAP_ABI_VERSION; }
 int lyap_self_test(void) { return 42; }
 
 const char* lyap_jit_note(void) { return lyap::jit_last_note(); }
+
+int lyap_selector_code(const lyap_params* p, int region, int64_t step, int* code) {
+    if (!code || region < 0 || region > 1) return fail(LYAP_ERR_INVALID, "lyap_selector_code: bad region or null output");
+    lyap::LambdaArgs a;
+    Geometry g;
+    if (int rc = build_args(p, &a, &g)) return rc;
+    const long long n = region ? a.iterations : a.warmup;
+    if (step < 0 || step >= n) return fail(LYAP_ERR_INVALID, "lyap_selector_code: step outside the region");
+    const int word0 = region ? a.acc_word0 : 0, wrap = region ? a.acc_wrap : a.wu_wrap;
+    *code = (int)((a.sel[word0 + (step / lyap::kStepsPerWord) % wrap] >> (2 * (step % lyap::kStepsPerWord))) & 3u);
+    return LYAP_OK;
+}
 
 const char* lyap_last_error(void) { return g_last_error.c_str(); }
 

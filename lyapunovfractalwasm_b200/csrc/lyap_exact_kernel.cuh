@@ -126,7 +126,7 @@ __device__ __forceinline__ double log_fast(double d, unsigned tab_addr, unsigned
 
 // careful_chunk for steps [first, first + n) of a region whose selector words start at `sel`.
 template <bool ACC>
-__device__ __noinline__ bool careful_steps(PixelState* ps, double rA, double rB, double rC, const unsigned* sel, int first,
+__device__ __noinline__ bool careful_steps(PixelState* ps, double rA, double rB, double rC, const unsigned* sel, int wrap, int first,
                                            int n, unsigned long long* steps) {
     bool dead = false;
     int j = first;
@@ -134,7 +134,7 @@ __device__ __noinline__ bool careful_steps(PixelState* ps, double rA, double rB,
     while (j < end && !dead) {
         const int in_word = j & (kStepsPerWord - 1);
         const int m = min(kStepsPerWord - in_word, end - j);
-        dead = careful_chunk<ACC>(ps, rA, rB, rC, sel[j / kStepsPerWord] >> (2 * in_word), m, steps);
+        dead = careful_chunk<ACC>(ps, rA, rB, rC, sel[(j / kStepsPerWord) % wrap] >> (2 * in_word), m, steps);
         j += m;
     }
     return dead;
@@ -362,6 +362,7 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
             const bool acc = region == 1;
             const int nsteps = acc ? a.iterations : a.warmup;
             const int word0 = acc ? a.acc_word0 : 0;
+            const int wrap = acc ? a.acc_wrap : a.wu_wrap;
             if constexpr (KG > 0) {
                 // specialised walk: chunks of CB whole periods (>= 16 steps), then the generic step for the rest
                 constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, CS = CB * BS;
@@ -395,7 +396,7 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                     } else {                      // less than one period: one step at a time
 #pragma unroll 1
                         for (int j = s; j < nsteps; ++j) {
-                            const unsigned code = (sel[j / kStepsPerWord] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
+                            const unsigned code = (sel[(j / kStepsPerWord) % wrap] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
                             if (acc) fast_group<P, true, HAS_C, 1>(x, lyap, rA, rB, rC, code, tab_addr, exp_addr);
                             else fast_group<P, false, HAS_C, 1>(x, lyap, rA, rB, rC, code, tab_addr, exp_addr);
                         }
@@ -409,8 +410,8 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                             my_steps += (unsigned long long)n;
                         } else {
                             PixelState ps{sx[p], sl[p], valid[p]};
-                            const bool dead = acc ? careful_steps<true>(&ps, rA[p], rB[p], rC, sel, s, n, &my_steps)
-                                                  : careful_steps<false>(&ps, rA[p], rB[p], rC, sel, s, n, &my_steps);
+                            const bool dead = acc ? careful_steps<true>(&ps, rA[p], rB[p], rC, sel, wrap, s, n, &my_steps)
+                                                  : careful_steps<false>(&ps, rA[p], rB[p], rC, sel, wrap, s, n, &my_steps);
                             x[p] = ps.x;
                             lyap[p] = ps.lyap;
                             valid[p] = ps.valid;
@@ -425,14 +426,15 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                 }
                 continue;
             }
-            const int nchunks = (nsteps + kStepsPerWord - 1) / kStepsPerWord;
-            for (int c = 0; c < nchunks; ++c) {
+            const int nchunks = nsteps / kStepsPerWord + (nsteps % kStepsPerWord != 0);
+            for (int c = 0, wi = 0; c < nchunks; ++c) {
                 bool all_done = true;
 #pragma unroll
                 for (int p = 0; p < P; ++p) all_done = all_done && done[p];
                 if (__all_sync(0xFFFFFFFFu, all_done)) break;
 
-                const unsigned word = a.sel[word0 + c];
+                const unsigned word = a.sel[word0 + wi];
+                if (++wi == wrap) wi = 0;
                 const int n = min(kStepsPerWord, nsteps - c * kStepsPerWord);
                 double sx[P], sl[P];
 #pragma unroll

@@ -12,6 +12,7 @@
 #include <dlfcn.h>
 #include <nvrtc.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -185,17 +186,23 @@ const char* jit_last_note() { return g_note.c_str(); }
 
 // Finds the group-pattern period of both regions of `a`.  Returns KG (1..16) and the two pattern words, or 0.
 int sequence_group_period(const LambdaArgs& a, unsigned long long* wu_pats, unsigned long long* acc_pats) {
-    auto code = [&](int word0, int i) { return (a.sel[word0 + i / kStepsPerWord] >> (2 * (i % kStepsPerWord))) & 3u; };
+    auto code = [&](bool acc_region, long long i) {
+        const int word0 = acc_region ? a.acc_word0 : 0, wrap = acc_region ? a.acc_wrap : a.wu_wrap;
+        return (a.sel[word0 + (i / kStepsPerWord) % wrap] >> (2 * (i % kStepsPerWord))) & 3u;
+    };
     for (int kg = 1; kg <= 16; ++kg) {
         const int bs = 2 * kg;
         bool ok = true;
-        for (int i = bs; i < a.warmup && ok; ++i) ok = code(0, i) == code(0, i - bs);
-        for (int i = bs; i < a.iterations && ok; ++i) ok = code(a.acc_word0, i) == code(a.acc_word0, i - bs);
+        // a wrapped region repeats after wrap words: one stored period plus bs steps covers every residue
+        const long long wu_n = std::min<long long>(a.warmup, (long long)a.wu_wrap * kStepsPerWord + bs);
+        const long long acc_n = std::min<long long>(a.iterations, (long long)a.acc_wrap * kStepsPerWord + bs);
+        for (long long i = bs; i < wu_n && ok; ++i) ok = code(false, i) == code(false, i - bs);
+        for (long long i = bs; i < acc_n && ok; ++i) ok = code(true, i) == code(true, i - bs);
         if (!ok) continue;
         unsigned long long wu = 0, acc = 0;
         for (int i = 0; i < bs; ++i) {
-            if (i < a.warmup) wu |= (unsigned long long)code(0, i) << (2 * i);
-            if (i < a.iterations) acc |= (unsigned long long)code(a.acc_word0, i) << (2 * i);
+            if (i < a.warmup) wu |= (unsigned long long)code(false, i) << (2 * i);
+            if (i < a.iterations) acc |= (unsigned long long)code(true, i) << (2 * i);
         }
         *wu_pats = wu;
         *acc_pats = acc;

@@ -68,7 +68,7 @@ static int exact_pixels_per_thread(long long n_pixels, int sm_count, int* thread
 cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                 int sm_count, cudaStream_t st) {
     bool has_c = false;
-    const int words = a.acc_word0 + (a.iterations + kStepsPerWord - 1) / kStepsPerWord;
+    const int words = a.acc_word0 + (a.iterations > 0 ? min(a.acc_wrap, (a.iterations - 1) / kStepsPerWord + 1) : 0);
     for (int i = 0; i < words; ++i) has_c = has_c || (a.sel[i] & 0xAAAAAAAAu);
 #define LYAP_VARIANT(P, T, U)                                                                    \
     (has_c ? launch_exact_variant<P, T, true, U>(a, out64, out32, steps, sm_count, st)            \

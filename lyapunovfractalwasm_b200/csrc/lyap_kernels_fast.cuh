@@ -101,7 +101,7 @@ __device__ __forceinline__ void fast_mode_steps(T (&x)[P], T (&prod)[P], const T
 
 // fast_careful_chunk for steps [first, first + n) of a region whose selector words start at `sel`.
 template <typename T, bool ACC>
-__device__ __noinline__ bool fast_careful_steps(FastPixel<T>* ps, T rA, T rB, T rC, const unsigned* sel, int first, int n,
+__device__ __noinline__ bool fast_careful_steps(FastPixel<T>* ps, T rA, T rB, T rC, const unsigned* sel, int wrap, int first, int n,
                                                 unsigned long long* steps) {
     bool dead = false;
     int j = first;
@@ -109,7 +109,7 @@ __device__ __noinline__ bool fast_careful_steps(FastPixel<T>* ps, T rA, T rB, T 
     while (j < end && !dead) {
         const int in_word = j & (kStepsPerWord - 1);
         const int m = min(kStepsPerWord - in_word, end - j);
-        dead = fast_careful_chunk<T, ACC>(ps, rA, rB, rC, sel[j / kStepsPerWord] >> (2 * in_word), m, steps);
+        dead = fast_careful_chunk<T, ACC>(ps, rA, rB, rC, sel[(j / kStepsPerWord) % wrap] >> (2 * in_word), m, steps);
         j += m;
     }
     return dead;
@@ -211,6 +211,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
             const bool acc = region == 1;
             const int nsteps = acc ? a.iterations : a.warmup;
             const int word0 = acc ? a.acc_word0 : 0;
+            const int wrap = acc ? a.acc_wrap : a.wu_wrap;
             if constexpr (KG > 0) {
                 constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, CS = CB * BS;
                 const unsigned* sel = a.sel + word0;
@@ -244,7 +245,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                     } else {
 #pragma unroll 1
                         for (int j = s; j < nsteps; ++j) {
-                            const unsigned code = (sel[j / kStepsPerWord] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
+                            const unsigned code = (sel[(j / kStepsPerWord) % wrap] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
                             if (acc) {
                                 if (code == 0) fast_mode_steps<T, P, true>(x, prod, rA);
                                 else if (code == 1) fast_mode_steps<T, P, true>(x, prod, rB);
@@ -270,8 +271,8 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             prod[p] = sp[p];
                             FastPixel<T> ps{sx[p], extra[p], valid[p]};
                             const bool dead =
-                                acc ? fast_careful_steps<T, true>(&ps, rA[p], rB[p], rC[p], sel, s, n, &my_steps)
-                                    : fast_careful_steps<T, false>(&ps, rA[p], rB[p], rC[p], sel, s, n, &my_steps);
+                                acc ? fast_careful_steps<T, true>(&ps, rA[p], rB[p], rC[p], sel, wrap, s, n, &my_steps)
+                                    : fast_careful_steps<T, false>(&ps, rA[p], rB[p], rC[p], sel, wrap, s, n, &my_steps);
                             x[p] = ps.x;
                             extra[p] = ps.extra;
                             valid[p] = ps.valid;
@@ -286,14 +287,15 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                 }
                 continue;
             }
-            const int nchunks = (nsteps + kStepsPerWord - 1) / kStepsPerWord;
-            for (int c = 0; c < nchunks; ++c) {
+            const int nchunks = nsteps / kStepsPerWord + (nsteps % kStepsPerWord != 0);
+            for (int c = 0, wi = 0; c < nchunks; ++c) {
                 bool all_done = true;
 #pragma unroll
                 for (int p = 0; p < P; ++p) all_done = all_done && done[p];
                 if (__all_sync(0xFFFFFFFFu, all_done)) break;
 
-                const unsigned word = a.sel[word0 + c];
+                const unsigned word = a.sel[word0 + wi];
+                if (++wi == wrap) wi = 0;
                 const int n = min(kStepsPerWord, nsteps - c * kStepsPerWord);
                 T sx[P], sp[P];
                 int se[P], emin[P], emax[P];

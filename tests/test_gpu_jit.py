@@ -99,3 +99,30 @@ def test_specialised_fast_kernels_agree_with_the_precompiled_ones(engine, jit_mo
         assert np.max(np.abs(got[0][0] - got[2][0])) < tol, case
         assert got[0][1] == got[2][1], case
     assert engine.lib.lyap_jit_note() == b""
+
+
+LONG_RUNS = [
+    dict(sequence="AB", iterations=20011, warmup=3001),                # beyond the 14336 steps the selector table holds:
+    dict(sequence="AABAB", iterations=30005, warmup=17),               # the regions are walked by the sequence's period
+    dict(sequence="BBBBBBAAAAAA", iterations=9000, warmup=9000),
+    dict(sequence="ABCAC", iterations=15000, warmup=2000, c=3.3),
+    dict(sequence="ABBABAABBBABAABABBBAABABAABBBABBAAABABBBABAABBABAAABBBABABBAABBAB", iterations=16000, warmup=1000),
+    dict(sequence="ABBABAABBBABAABABBBAABABAABBBABBAAABABBBABAABBABAAABBBABABBAABBABA", iterations=16001, warmup=999),
+]
+
+
+@pytest.mark.parametrize("case", LONG_RUNS, ids=lambda c: "%d_%d_%d" % (len(c["sequence"]), c["iterations"], c["warmup"]))
+def test_runs_longer_than_the_selector_table(engine, port, jit_mode, case):
+    """Specialised and precompiled kernels, exact mode, bit for bit; the fast modes on the same frame to their tolerance."""
+    kw = dict(min_x=2.4, max_x=4.0, min_y=2.4, max_y=4.0, width=50, height=21, **case)
+    want, steps = oracle(port, kw)
+    for mode in (2, 0):
+        jit_mode(mode)
+        r = engine.render(L.make_params(**kw), want=("lambda",))
+        assert np.array_equal(r["lambda"].view(np.uint64), want.view(np.uint64)), mode
+        assert r["stats"].executed_steps == steps, mode
+        for fast, tol in ((L.MODE_FAST_FP64, 1e-9), (L.MODE_FAST_FP32, 5e-2)):
+            f = engine.render(L.make_params(**kw, mode=fast), want=("lambda",))["lambda"][:-1, :-1]
+            w = want[:-1, :-1]
+            assert np.array_equal(f == -5.0, w == -5.0)
+            assert np.median(np.abs(f - w)) < tol, (mode, fast)
