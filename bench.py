@@ -1,13 +1,16 @@
 #!/usr/bin/env python3
 """Benchmark of the Lyapunov-fractal hot path on B200s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode exact|fast64|fast32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode exact|fast64|fast32] [--impl reference] [--config 3|4]
 
 One "step" renders one frame end to end on the device: lambda kernel -> min/max -> normalise -> colour.
 Workload at N = 1: the 4096x4096 "AABAB" frame, 200 warm-up + 2000 accumulated steps per pixel, exact fp64.
 At N > 1 (one process per GPU, launched by torch.distributed.run) the frame grows to 4096 x (4096*N) and
 each rank renders one 4096-row band (weak scaling); the only exchange is the all-reduce of the frame's
 min/max (two doubles) before the colour stage, and each rank recomputes its two halo rows.
+
+--config 3 (16384^2, "BBBBBBAAAAAA", 500 + 4000) and --config 4 (65536^2, "AB", 100 + 1000) render that one frame
+split into N row bands instead (strong scaling; device-resident only, no end-to-end leg at those sizes).
 
 Metric: logistic-map steps per second (executed steps of all ranks / max-over-ranks device time).
 PyTorch appears here only as plumbing: CUDA events on the launching stream, pinned host buffers,
@@ -27,6 +30,10 @@ sys.path.insert(0, ROOT)
 
 CFG2 = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=4096, height=4096, sequence="AABAB",
             iterations=2000, warmup=200)
+CFG3 = dict(min_x=3.4, max_x=4.0, min_y=2.5, max_y=3.4, width=16384, height=16384, sequence="BBBBBBAAAAAA",
+            iterations=4000, warmup=500)
+CFG4 = dict(min_x=2.0, max_x=4.0, min_y=2.0, max_y=4.0, width=65536, height=65536, sequence="AB",
+            iterations=1000, warmup=100)
 # fp64 instructions per logistic step in the exact kernel's main path, counted from its source:
 #   warm-up step      3  (r*x, 1-x, product)
 #   accumulated step 13  (fma(-2,x,1), r*|.|, 7 for the log incl. its last addition, sum +=, r*x, 1-x, product)
@@ -165,6 +172,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--mode", default="exact", choices=["exact", "fast64", "fast32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
+                    help="2 (default): the 4096-wide frame, one 4096-row band per GPU; 3, 4: that frame split over the GPUs")
     ap.add_argument("--no-gather", action="store_true", help="skip the optional NCCL gather of the RGBA bands to rank 0 (N > 1)")
     args = ap.parse_args()
 
@@ -193,7 +202,8 @@ def main():
     mode = {"exact": L.MODE_EXACT, "fast64": L.MODE_FAST_FP64, "fast32": L.MODE_FAST_FP32}[args.mode]
 
     # the frame: cfg2 at N = 1; N bands of 4096 rows at N > 1
-    kw = dict(CFG2, height=CFG2["height"] * world, mode=mode)
+    strong = args.config != 2
+    kw = dict({3: CFG3, 4: CFG4}[args.config], mode=mode) if strong else dict(CFG2, height=CFG2["height"] * world, mode=mode)
     width, height = kw["width"], kw["height"]
     b0, b1 = bands.band_rows(height, world, rank)
     above, below = bands.halo_rows(height, b0, b1)
@@ -264,42 +274,45 @@ def main():
     value = executed_all / (ms * 1e-3)
 
     # ---- end to end: same frame through the host-buffer path, copies inside the timed region ----
-    h_norm = torch.empty(rows_own * width, dtype=torch.float64).pin_memory()
-    h_rgba = torch.empty(rows_own * width * 4, dtype=torch.uint8).pin_memory()
-    p_full = L.make_params(**kw)
-    stats = L.RenderStats()
+    def end_to_end():
+        h_norm = torch.empty(rows_own * width, dtype=torch.float64).pin_memory()
+        h_rgba = torch.empty(rows_own * width * 4, dtype=torch.uint8).pin_memory()
+        p_full = L.make_params(**kw)
+        stats = L.RenderStats()
 
-    def e2e_step():
-        if world == 1:
-            # the call a user makes: lyap_render with host pointers (parameters in, normalised + RGBA out)
-            L._check(eng.lib.lyap_render(eng.ctx, ctypes.byref(p_full), None, None, h_norm.data_ptr(),
-                                         h_rgba.data_ptr(), None, ctypes.byref(stats)))
-            return stats.executed_steps
-        step()
-        L._check(eng.lib.lyap_copy_to_host(eng.ctx, h_norm.data_ptr(), d_norm.data_ptr() + own_off, rows_own * width * 8))
-        L._check(eng.lib.lyap_copy_to_host(eng.ctx, h_rgba.data_ptr(), d_rgba.data_ptr(), rows_own * width * 4))
-        return None
+        def e2e_step():
+            if world == 1:
+                # the call a user makes: lyap_render with host pointers (parameters in, normalised + RGBA out)
+                L._check(eng.lib.lyap_render(eng.ctx, ctypes.byref(p_full), None, None, h_norm.data_ptr(),
+                                             h_rgba.data_ptr(), None, ctypes.byref(stats)))
+                return stats.executed_steps
+            step()
+            L._check(eng.lib.lyap_copy_to_host(eng.ctx, h_norm.data_ptr(), d_norm.data_ptr() + own_off, rows_own * width * 8))
+            L._check(eng.lib.lyap_copy_to_host(eng.ctx, h_rgba.data_ptr(), d_rgba.data_ptr(), rows_own * width * 4))
+            return None
 
-    e2e_step()
-    barrier()
-    d_steps.zero_()
-    ev0.record(stream)
-    te = time.perf_counter()
-    e2e_executed = 0
-    for _ in range(args.steps):
-        r = e2e_step()
-        e2e_executed += r if r is not None else 0
-    ev1.record(stream)
-    torch.cuda.synchronize()
-    wall_ms = (time.perf_counter() - te) * 1e3
-    if world > 1:
-        e2e_executed = int(d_steps.item()) * rows_own // rows_all
-    t = torch.tensor([wall_ms], dtype=torch.float64, device=dev)
-    s = torch.tensor([e2e_executed], dtype=torch.int64, device=dev)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(s, op=dist.ReduceOp.SUM)
-    e2e_value = int(s[0]) / (float(t[0]) * 1e-3)
+        e2e_step()
+        barrier()
+        d_steps.zero_()
+        ev0.record(stream)
+        te = time.perf_counter()
+        e2e_executed = 0
+        for _ in range(args.steps):
+            r = e2e_step()
+            e2e_executed += r if r is not None else 0
+        ev1.record(stream)
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - te) * 1e3
+        if world > 1:
+            e2e_executed = int(d_steps.item()) * rows_own // rows_all
+        t = torch.tensor([wall_ms], dtype=torch.float64, device=dev)
+        s = torch.tensor([e2e_executed], dtype=torch.int64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(s, op=dist.ReduceOp.SUM)
+        return int(s[0]) / (float(t[0]) * 1e-3)
+
+    e2e_value = None if strong else end_to_end()
 
     # ---- optional: gather the finished RGBA bands to rank 0 over NCCL (outside the timed regions above) ----
     gather = None
@@ -344,24 +357,30 @@ def main():
             "ms_per_launch": ms_lambda,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch on the 4096x4096 frame (ncu, profiles/):
             # 2.3 MB read + 76.9 MB written; less than the 134 MB of stores because the tail is still in L2 at kernel end
-            "traffic": 79.2e6 * rows_all / 4096 if mode == L.MODE_EXACT else None,
+            "traffic": 79.2e6 * rows_all / 4096 if mode == L.MODE_EXACT and not strong else None,
             "hbm": {"algorithmic_bytes_per_launch": out_bytes, "store_gbs": out_bytes / (ms_lambda * 1e-3) / 1e9,
                     "peak_gbs": hbm_peak, "peak_source": "MEASURED_PEAKS.json (measured)" if hbm_peak else "absent"},
         }
+        what = "%s mode; step = lambda + min/max + normalise + RGBA8 on the device" % args.mode
+        if strong:
+            workload = ("cfg%d: %dx%d '%s', %d warm-up + %d accumulated steps, %s; the one frame as %d row band(s) of %d rows"
+                        % (args.config, width, height, kw["sequence"], kw["warmup"], kw["iterations"], what, world, rows_own))
+        else:
+            workload = ("cfg2: 4096x4096 'AABAB', a,b in [2.5,4], 200 warm-up + 2000 accumulated steps, " + what
+                        + ("" if world == 1 else "; frame 4096x%d as %d row bands of 4096 rows, halo rows "
+                           "recomputed and excluded from the step count pro rata" % (height, world)))
         line = {
             "metric": "logistic-map steps/s", "value": value, "unit": "steps/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "f32" if mode == L.MODE_FAST_FP32 else "f64", "data": "synthetic",
-            "config": {"workload": "cfg2: 4096x4096 'AABAB', a,b in [2.5,4], 200 warm-up + 2000 accumulated steps, "
-                                   "%s mode; step = lambda + min/max + normalise + RGBA8 on the device" % args.mode
-                                   + ("" if world == 1 else "; frame 4096x%d as %d row bands of 4096 rows, halo rows "
-                                      "recomputed and excluded from the step count pro rata" % (height, world)),
+            "config": {"workload": workload,
                        "l2": "each step rewrites %.0f MiB of outputs per GPU (> 126 MB L2); the path has no input arrays"
                              % ((rows_all * width * 16 + rows_own * width * 4) / 2 ** 20),
                        "executed_over_nominal": executed_all / (args.steps * width * height * (kw["warmup"] + kw["iterations"]))},
-            "ms_per_frame_4096": ms / args.steps,
+            ("ms_per_frame" if strong else "ms_per_frame_4096"): ms / args.steps,
             "roofline": roofline,
-            "e2e": {"value": e2e_value, "unit": "steps/s", "h2d_bytes_per_step": ctypes.sizeof(L.LyapParams) + len(kw["sequence"]),
+            "e2e": None if e2e_value is None else {"value": e2e_value, "unit": "steps/s", "h2d_bytes_per_step": ctypes.sizeof(L.LyapParams) + len(kw["sequence"]),
                     "d2h_bytes_per_step": rows_own * width * 12 + ctypes.sizeof(L.RenderStats),
                     "what": "lyap_render(host pointers): parameters in, normalised fp64 + RGBA8 frame out to pinned host memory"
                             if world == 1 else "band path + lyap_copy_to_host of the band's normalised fp64 + RGBA8"},
