@@ -177,6 +177,18 @@ int lyap_render(lyap_ctx* ctx, const lyap_params* p, double* out_lambda, float* 
 int lyap_render_multi(const lyap_params* p, int32_t n_devices, const int32_t* devices, double* out_lambda,
                       double* out_norm, uint8_t* out_rgba, double timeout_seconds, lyap_render_stats* stats);
 
+/* A batch of independent whole frames -- a zoom sequence: each frame its own window, hence its own min/max
+ * (the page calls computeLyapunovFractal once per view, web/fractal_renderer.js:132-154) -- dealt round-robin to
+ * the listed devices: frame k goes to devices[k % n_devices].  One worker thread and one context per device;
+ * on each device the kernels of successive frames run back to back on one stream while the previous frame's
+ * outputs are copied to the host on a second stream from a second set of buffers, so copies cost no device time
+ * as long as they are shorter than a frame.  out_norm / out_rgba are arrays of n_frames host pointers (either
+ * array, or single entries, may be NULL; pinned memory from lyap_host_alloc copies fastest); stats, if given,
+ * is an array of n_frames records (ms_copies = time from the frame's last kernel to its last byte on the host).
+ * Every frame's bytes equal those of lyap_render on that frame. */
+int lyap_render_frames(const lyap_params* frames, int32_t n_frames, int32_t n_devices, const int32_t* devices,
+                       double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats);
+
 /* ---- for callers that must not allocate ---- */
 
 /* No counterpart in the reference.  Same result as lyap_minmax_device, for hosts that are not allowed to

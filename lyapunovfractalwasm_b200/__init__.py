@@ -5,6 +5,7 @@ thin Python binding the tests and the benchmark drive it through.  It holds no c
 fallback: if the library is missing or no CUDA device answers, calls raise.
 """
 import ctypes
+import weakref
 import os
 
 import numpy as np
@@ -90,6 +91,9 @@ ABI = {
                                    ctypes.POINTER(RenderStats)]),
     "lyap_render_multi": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), _P, _P,
                                          _P, ctypes.c_double, ctypes.POINTER(RenderStats)]),
+    "lyap_render_frames": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.c_int32, ctypes.c_int32,
+                                          ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(_P), ctypes.POINTER(_P),
+                                          ctypes.POINTER(RenderStats)]),
     "lyap_minmax_device_noalloc": (ctypes.c_int, [_P, ctypes.c_uint64, _P, _P]),
     "lyap_fp64_peak": (ctypes.c_int, [_P, c_double_p]),
     "lyap_fp32_peak": (ctypes.c_int, [_P, c_double_p]),
@@ -151,6 +155,43 @@ NOALLOC_MAX_VALUES = 1 << 32
 def minmax_device_noalloc(d_values, n, d_minmax, cuda_stream=None):
     """lyap_minmax_device_noalloc on the current device: no context, no allocation (see include/lyap_b200.h)."""
     _check(load_library().lyap_minmax_device_noalloc(d_values, n, d_minmax, cuda_stream))
+
+
+def render_frames(frames, devices, want=("norm", "rgba"), pinned=False):
+    """lyap_render_frames: a list of lyap_params (whole frames) dealt round-robin to the device ordinals.
+    Returns ({"norm": [array per frame], "rgba": [...]}, [RenderStats per frame]); with pinned=True the output
+    arrays live in page-locked memory (lyap_host_alloc) that is released when the returned arrays are collected."""
+    lib = load_library()
+    n = len(frames)
+    arr = (LyapParams * n)()
+    keep = []
+    for i, f in enumerate(frames):
+        ctypes.memmove(ctypes.byref(arr[i]), ctypes.byref(f), ctypes.sizeof(LyapParams))
+        keep.append(f)           # the sequence bytes the copies point to
+
+    def host_array(shape, dtype):
+        if not pinned:
+            return np.empty(shape, dtype=dtype)
+        nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        ptr = ctypes.c_void_p()
+        _check(lib.lyap_host_alloc(ctypes.byref(ptr), nbytes))
+        buf = (ctypes.c_uint8 * nbytes).from_address(ptr.value)
+        a = np.frombuffer(buf, dtype=dtype).reshape(shape)
+        weakref.finalize(buf, lib.lyap_host_free, ptr)
+        return a
+
+    out, ptrs = {}, {}
+    for key, dtype, tail in (("norm", np.float64, ()), ("rgba", np.uint8, (4,))):
+        if key in want:
+            out[key] = [host_array((f.height, f.width) + tail, dtype) for f in frames]
+            ptrs[key] = (_P * n)(*[a.ctypes.data for a in out[key]])
+        else:
+            ptrs[key] = None
+    devs = (ctypes.c_int32 * len(devices))(*devices)
+    stats = (RenderStats * n)()
+    _check(lib.lyap_render_frames(arr, n, len(devices), devs, ptrs["norm"], ptrs["rgba"], stats))
+    del keep
+    return out, list(stats)
 
 
 def render_multi(params, devices, want=("lambda", "norm", "rgba"), timeout_seconds=0.0):

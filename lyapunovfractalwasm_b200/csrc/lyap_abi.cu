@@ -712,6 +712,173 @@ extern "C" int lyap_render_multi(const lyap_params* p, int32_t n_devices, const 
     return LYAP_OK;
 }
 
+// ---- a batch of independent frames (a zoom sequence) over several devices ----
+
+namespace {
+
+struct FramesShared {
+    std::mutex mu;
+    bool failed = false;
+    int status = LYAP_OK;
+    std::string error;
+};
+
+void frames_fail(FramesShared& sh, int status, const char* msg) {
+    std::lock_guard<std::mutex> lk(sh.mu);
+    if (sh.status == LYAP_OK) {
+        sh.status = status;
+        sh.error = msg;
+    }
+    sh.failed = true;
+}
+
+struct FrameSmall {
+    double mm[2];
+    unsigned long long steps;
+};
+
+// One set of device buffers; a worker alternates between two, so that one frame's copies to the host run
+// while the next frame is computed.
+struct FrameSlot {
+    void *lam = nullptr, *norm = nullptr, *rgba = nullptr, *small = nullptr;
+    FrameSmall* h_small = nullptr;   // pinned
+    cudaEvent_t begun = nullptr, lambda_done = nullptr, computed = nullptr, copied = nullptr;
+    int frame = -1;
+};
+
+// Frames first, first + stride, ... on one device: kernels in order on the context's stream, copies on a second
+// stream behind an event, two buffer sets.
+void frames_worker(FramesShared& sh, int device, int first, int stride, const lyap_params* frames, int n_frames,
+                   double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats) {
+    lyap_ctx* c = nullptr;
+    if (lyap_create(&c, device) != LYAP_OK) return frames_fail(sh, LYAP_ERR_CUDA, lyap_last_error());
+    cudaStream_t copy = nullptr;
+    FrameSlot slots[2];
+    size_t max_px = 0;
+    bool any_rgba = false;
+    for (int k = first; k < n_frames; k += stride) {
+        max_px = std::max(max_px, (size_t)frames[k].width * (size_t)frames[k].height);
+        any_rgba = any_rgba || (out_rgba && out_rgba[k]);
+    }
+    auto cleanup = [&]() {
+        cudaStreamSynchronize(c->stream);
+        if (copy) cudaStreamSynchronize(copy);
+        for (FrameSlot& s : slots) {
+            for (void* q : {s.lam, s.norm, s.rgba, s.small})
+                if (q) cudaFree(q);
+            if (s.h_small) cudaFreeHost(s.h_small);
+            for (cudaEvent_t e : {s.begun, s.lambda_done, s.computed, s.copied})
+                if (e) cudaEventDestroy(e);
+        }
+        if (copy) cudaStreamDestroy(copy);
+        lyap_destroy(c);
+    };
+    auto bail_cuda = [&](cudaError_t e, const char* what) {
+        fail_cuda(e, what);
+        frames_fail(sh, LYAP_ERR_CUDA, lyap_last_error());
+        cleanup();
+    };
+#define FR(call)                                                   \
+    do {                                                           \
+        cudaError_t fr_e = (call);                                 \
+        if (fr_e != cudaSuccess) return bail_cuda(fr_e, #call);    \
+    } while (0)
+    FR(cudaStreamCreateWithFlags(&copy, cudaStreamNonBlocking));
+    for (FrameSlot& s : slots) {
+        FR(cudaMalloc(&s.lam, max_px * 8));
+        FR(cudaMalloc(&s.norm, max_px * 8));
+        if (any_rgba) FR(cudaMalloc(&s.rgba, max_px * 4));
+        FR(cudaMalloc(&s.small, 32));
+        FR(cudaMallocHost(reinterpret_cast<void**>(&s.h_small), sizeof(FrameSmall)));
+        for (cudaEvent_t* e : {&s.begun, &s.lambda_done, &s.computed, &s.copied}) FR(cudaEventCreate(e));
+    }
+    // the slot's frame has reached the host: fill in its statistics
+    auto finish = [&](FrameSlot& s) -> cudaError_t {
+        if (s.frame < 0) return cudaSuccess;
+        cudaError_t e = cudaEventSynchronize(s.copied);
+        if (e != cudaSuccess) return e;
+        if (stats) {
+            const lyap_params& p = frames[s.frame];
+            lyap_render_stats& r = stats[s.frame];
+            std::memset(&r, 0, sizeof(r));
+            r.executed_steps = s.h_small->steps;
+            r.nominal_steps = (uint64_t)p.width * (uint64_t)p.height * (uint64_t)((long long)p.warmup + p.iterations);
+            r.lambda_min = s.h_small->mm[0];
+            r.lambda_max = s.h_small->mm[1];
+            cudaEventElapsedTime(&r.ms_lambda, s.begun, s.lambda_done);
+            cudaEventElapsedTime(&r.ms_total_device, s.begun, s.computed);
+            cudaEventElapsedTime(&r.ms_copies, s.computed, s.copied);
+            r.kernel_launches = (out_rgba && out_rgba[s.frame]) ? 4 : 3;
+        }
+        s.frame = -1;
+        return cudaSuccess;
+    };
+    int local = 0;
+    for (int k = first; k < n_frames; k += stride, ++local) {
+        {
+            std::lock_guard<std::mutex> lk(sh.mu);
+            if (sh.failed) break;
+        }
+        FrameSlot& s = slots[local & 1];
+        FR(finish(s));   // its buffers are free again
+        const lyap_params& p = frames[k];
+        const size_t n = (size_t)p.width * (size_t)p.height;
+        double* d_mm = static_cast<double*>(s.small);
+        uint64_t* d_steps = reinterpret_cast<uint64_t*>(d_mm + 2);
+        cudaStream_t st = c->stream;
+        FR(cudaMemsetAsync(d_steps, 0, 8, st));
+        FR(cudaEventRecord(s.begun, st));
+        int rc = lyap_lambda_device(c, &p, static_cast<double*>(s.lam), nullptr, d_steps);
+        if (rc == LYAP_OK) {
+            FR(cudaEventRecord(s.lambda_done, st));
+            rc = lyap_minmax_device(c, static_cast<double*>(s.lam), n, d_mm);
+        }
+        if (rc == LYAP_OK) rc = lyap_normalize_device(c, static_cast<double*>(s.lam), n, d_mm, static_cast<double*>(s.norm));
+        uint8_t* h_rgba = out_rgba ? out_rgba[k] : nullptr;
+        double* h_norm = out_norm ? out_norm[k] : nullptr;
+        if (rc == LYAP_OK && h_rgba)
+            rc = lyap_colorize_device(c, static_cast<double*>(s.norm), p.width, p.height, 0, 0, p.palette, static_cast<uint8_t*>(s.rgba));
+        if (rc != LYAP_OK) {
+            frames_fail(sh, rc, lyap_last_error());
+            cleanup();
+            return;
+        }
+        FR(cudaEventRecord(s.computed, st));
+        FR(cudaStreamWaitEvent(copy, s.computed, 0));
+        if (h_norm) FR(cudaMemcpyAsync(h_norm, s.norm, n * 8, cudaMemcpyDeviceToHost, copy));
+        if (h_rgba) FR(cudaMemcpyAsync(h_rgba, s.rgba, n * 4, cudaMemcpyDeviceToHost, copy));
+        FR(cudaMemcpyAsync(s.h_small, s.small, sizeof(FrameSmall), cudaMemcpyDeviceToHost, copy));
+        FR(cudaEventRecord(s.copied, copy));
+        s.frame = k;
+    }
+    for (FrameSlot& s : slots) FR(finish(s));
+#undef FR
+    cleanup();
+}
+
+}  // namespace
+
+extern "C" int lyap_render_frames(const lyap_params* frames, int32_t n_frames, int32_t n_devices, const int32_t* devices,
+                                  double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats) {
+    if (n_frames < 0 || (n_frames > 0 && !frames)) return fail(LYAP_ERR_INVALID, "lyap_render_frames: bad frame list");
+    if (n_devices < 1 || !devices) return fail(LYAP_ERR_INVALID, "need at least one device");
+    for (int k = 0; k < n_frames; ++k) {
+        lyap::LambdaArgs a;
+        Geometry g;
+        if (int r = build_args(&frames[k], &a, &g)) return r;
+        if (g.rows != frames[k].height)
+            return fail(LYAP_ERR_INVALID, "lyap_render_frames renders whole frames (row_begin = row_end = 0)");
+    }
+    FramesShared sh;
+    std::vector<std::thread> workers;
+    for (int r = 0; r < n_devices && r < n_frames; ++r)
+        workers.emplace_back(frames_worker, std::ref(sh), (int)devices[r], r, (int)n_devices, frames, (int)n_frames, out_norm,
+                             out_rgba, stats);
+    for (auto& w : workers) w.join();
+    if (sh.status != LYAP_OK) return fail(sh.status, sh.error);
+    return LYAP_OK;
+}
+
 extern "C" {
 
 int lyap_glow(lyap_ctx* c, const uint8_t* rgba_in, int32_t width, int32_t height, uint8_t* rgba_out) {

@@ -5,6 +5,9 @@
 // (web/index.html:110-124; defaults "AB", 1000), palette "cosmic".  --config N selects one of the five
 // benchmark configurations.  Output: one JSON line with timings; --out writes the frame (.ppm = RGB,
 // .rgba = raw RGBA8, .f64 = raw normalised doubles, the array the WASM export returns).
+// --config 5 --frames N renders N frames of the zoom batch, starting at --frame, dealt round-robin to the
+// GPUs (lyap_render_frames); --out name.ppm then writes name.0000.ppm, name.0001.ppm, ...
+#include <algorithm>
 #include <charconv>
 #include <chrono>
 #include <cmath>
@@ -28,13 +31,13 @@ struct Options {
     std::string sequence = "AB", palette = "cosmic", mode = "exact", out;
     bool has_c = false;
     double c = 0.0;
-    int gpus = 1, frame = 0;
+    int gpus = 1, frame = 0, frames = 0;
     bool glow = false;
 };
 
 [[noreturn]] void usage(const char* why) {
     std::cerr << "lyap_cli: " << why << "\n"
-              << "usage: lyap_cli [--config 1..5 [--frame K]] [--width W --height H --min-x .. --max-x .. --min-y .. --max-y ..]\n"
+              << "usage: lyap_cli [--config 1..5 [--frame K] [--frames N]] [--width W --height H --min-x .. --max-x .. --min-y .. --max-y ..]\n"
               << "                [--sequence S] [--iterations N] [--warmup N] [--c V] [--palette NAME]\n"
               << "                [--mode exact|fast64|fast32] [--gpus N] [--glow] [--out file.ppm|.rgba|.f64]\n";
     std::exit(2);
@@ -69,6 +72,75 @@ int to_int(std::string_view s) {
     return v;
 }
 
+void write_frame(const std::string& path, const uint8_t* rgba, int width, int height) {
+    std::ofstream f(path, std::ios::binary);
+    if (!f) { std::cerr << "lyap_cli: cannot write " << path << "\n"; std::exit(1); }
+    const size_t n = static_cast<size_t>(width) * static_cast<size_t>(height);
+    if (path.ends_with(".ppm")) {
+        f << std::format("P6\n{} {}\n255\n", width, height);
+        std::vector<uint8_t> rgb(n * 3);
+        for (size_t i = 0; i < n; ++i) { rgb[3 * i] = rgba[4 * i]; rgb[3 * i + 1] = rgba[4 * i + 1]; rgb[3 * i + 2] = rgba[4 * i + 2]; }
+        f.write(reinterpret_cast<const char*>(rgb.data()), static_cast<std::streamsize>(rgb.size()));
+    } else {
+        f.write(reinterpret_cast<const char*>(rgba), static_cast<std::streamsize>(n * 4));
+    }
+}
+
+// Frames o.frame .. o.frame + o.frames - 1 of the zoom batch: window half-width 0.5*0.97^k around (3.82, 3.45),
+// everything else as given (size, sequence, c, palette, mode).
+int render_zoom_batch(const Options& o, const lyap_params& base) {
+    const int nf = o.frames;
+    std::vector<lyap_params> frames(nf, base);
+    for (int i = 0; i < nf; ++i) {
+        const double h = 0.5 * std::pow(0.97, o.frame + i);
+        frames[i].min_x = 3.82 - h; frames[i].max_x = 3.82 + h;
+        frames[i].min_y = 3.45 - h; frames[i].max_y = 3.45 + h;
+    }
+    const size_t bytes = static_cast<size_t>(o.width) * static_cast<size_t>(o.height) * 4;
+    std::vector<uint8_t*> rgba(nf, nullptr);
+    for (int i = 0; i < nf; ++i) {
+        void* q = nullptr;
+        if (lyap_host_alloc(&q, bytes) != LYAP_OK) {
+            std::cerr << "lyap_cli: " << lyap_last_error() << "\n";
+            return 1;
+        }
+        rgba[i] = static_cast<uint8_t*>(q);
+    }
+    std::vector<int32_t> devs(std::max(1, o.gpus));
+    for (size_t i = 0; i < devs.size(); ++i) devs[i] = static_cast<int32_t>(i);
+    std::vector<lyap_render_stats> st(nf);
+    const auto t0 = std::chrono::steady_clock::now();
+    const int status = lyap_render_frames(frames.data(), nf, static_cast<int32_t>(devs.size()), devs.data(), nullptr,
+                                          rgba.data(), st.data());
+    const double wall_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (status != LYAP_OK) {
+        std::cerr << "lyap_cli: " << lyap_status_string(status) << ": " << lyap_last_error() << "\n";
+        return 1;
+    }
+    uint64_t executed = 0, nominal = 0;
+    double ms_lambda = 0, ms_device = 0;
+    for (const auto& s : st) {
+        executed += s.executed_steps;
+        nominal += s.nominal_steps;
+        ms_lambda += s.ms_lambda;
+        ms_device += s.ms_total_device;
+    }
+    if (!o.out.empty()) {
+        const size_t dot = o.out.rfind('.');
+        for (int i = 0; i < nf; ++i)
+            write_frame(std::format("{}.{:04d}{}", o.out.substr(0, dot), o.frame + i, dot == std::string::npos ? "" : o.out.substr(dot)),
+                        rgba[i], o.width, o.height);
+    }
+    for (uint8_t* q : rgba) lyap_host_free(q);
+    std::cout << std::format(
+        "{{\"frames\": {}, \"first_frame\": {}, \"width\": {}, \"height\": {}, \"sequence\": \"{}\", \"mode\": \"{}\", "
+        "\"gpus\": {}, \"executed_steps\": {}, \"nominal_steps\": {}, \"ms_lambda_sum\": {:.3f}, \"ms_device_sum\": {:.3f}, "
+        "\"ms_wall\": {:.3f}, \"frames_per_s_wall\": {:.2f}, \"steps_per_s_wall\": {:.4e}}}\n",
+        nf, o.frame, o.width, o.height, o.sequence, o.mode, devs.size(), executed, nominal, ms_lambda, ms_device, wall_ms,
+        nf / (wall_ms * 1e-3), executed / (wall_ms * 1e-3));
+    return 0;
+}
+
 }  // namespace
 
 int main(int argc, char** argv) {
@@ -85,6 +157,7 @@ int main(int argc, char** argv) {
         };
         if (a == "--config") { const int fr = o.frame; o.frame = fr; apply_config(o, to_int(next())); }
         else if (a == "--frame") next();
+        else if (a == "--frames") o.frames = to_int(next());
         else if (a == "--width") o.width = to_int(next());
         else if (a == "--height") o.height = to_int(next());
         else if (a == "--min-x") o.min_x = to_double(next());
@@ -114,6 +187,8 @@ int main(int argc, char** argv) {
     p.palette = lyap_palette_from_name(o.palette.c_str());
     p.c_enabled = o.has_c ? 1 : 0;
     p.c_value = o.c;
+
+    if (o.frames > 0) return render_zoom_batch(o, p);
 
     const size_t n = static_cast<size_t>(o.width) * static_cast<size_t>(o.height);
     const bool want_f64 = o.out.ends_with(".f64");

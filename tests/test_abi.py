@@ -83,3 +83,10 @@ def test_fails_loudly_without_a_device():
     with pytest.raises(L.LyapError) as ei:
         L.Engine(0)
     assert ei.value.status == 4
+    frames = [L.make_params(width=8, height=8, sequence="AB", iterations=10, warmup=2) for _ in range(3)]
+    with pytest.raises(L.LyapError) as ei:          # the batch entry point: same rule, reported from its worker thread
+        L.render_frames(frames, [0])
+    assert ei.value.status == 4
+    with pytest.raises(L.LyapError) as ei:          # argument errors come before any device is touched
+        L.render_frames([L.make_params(width=8, height=8, sequence="", iterations=10, warmup=2)], [0])
+    assert ei.value.status == 2

@@ -192,3 +192,33 @@ def test_glow_matches_the_cpu_restatement(engine, port):
     tiny[..., 3] = 255
     tiny[1, 2, :3] = 200
     assert np.array_equal(engine.glow(tiny), port.glow(tiny))
+
+
+def test_render_frames_batch_equals_frame_by_frame(engine, port):
+    """lyap_render_frames (two buffer sets, copies on their own stream) against lyap_render frame by frame and the
+    oracle: frames of different sizes and sequences, more frames than buffer sets, the same device listed twice."""
+    from conftest import config5_frame
+    frames_kw = [dict(config5_frame(k), width=320, height=180, iterations=300, warmup=30) for k in (0, 20, 40, 60, 80)]
+    frames_kw.insert(2, dict(min_x=2.0, max_x=4.0, min_y=2.0, max_y=4.0, width=257, height=131, sequence="AB",
+                             iterations=200, warmup=20))
+    frames_kw.append(dict(min_x=0.0, max_x=4.0, min_y=0.0, max_y=4.0, width=64, height=48, sequence="BBA",
+                          iterations=100, warmup=10, palette=3))
+    frames = [L.make_params(**kw) for kw in frames_kw]
+    for devices, pinned in (([0], False), ([0, 0], True)):
+        out, stats = L.render_frames(frames, devices, pinned=pinned)
+        for i, kw in enumerate(frames_kw):
+            one = engine.render(frames[i], want=("norm", "rgba"))
+            assert np.array_equal(out["norm"][i].view(np.uint64), one["norm"].view(np.uint64)), i
+            assert np.array_equal(out["rgba"][i], one["rgba"]), i
+            st = stats[i]
+            assert st.executed_steps == one["stats"].executed_steps and st.nominal_steps == one["stats"].nominal_steps
+            assert (st.lambda_min, st.lambda_max) == (one["stats"].lambda_min, one["stats"].lambda_max)
+            assert st.ms_lambda > 0 and st.ms_total_device >= st.ms_lambda and st.ms_copies > 0
+        lam, _ = port.lambda_rows(*[frames_kw[2][k] for k in ("min_x", "max_x", "min_y", "max_y", "width", "height",
+                                                               "sequence", "iterations", "warmup")])
+        assert np.array_equal(out["norm"][2].view(np.uint64), port.normalize(lam).view(np.uint64))
+    # only RGBA wanted; no frames at all
+    out, stats = L.render_frames(frames[:3], [0], want=("rgba",))
+    assert "norm" not in out and np.array_equal(out["rgba"][1], engine.render(frames[1], want=("rgba",))["rgba"])
+    out, stats = L.render_frames([], [0])
+    assert out == {"norm": [], "rgba": []} and stats == []
