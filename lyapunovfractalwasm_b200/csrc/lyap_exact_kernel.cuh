@@ -97,18 +97,21 @@ struct LogConsts {
 __constant__ LogConsts c_logk = {LYAP_LOG_C2, LYAP_LOG_C3, LYAP_LOG_C4, LYAP_LN2HI, LYAP_LN2LO, LYAP_KLO_BIAS};
 __constant__ int c_minus_2p20 = -(1 << 20);   // read as a constant-bank operand so the product below stays one multiply-add
 
-// lyap_log_core (lyap_math.h) for a positive normal d, written against the two shared-memory tables:
-// `tab_addr` is the shared-window byte address of this lane's copy of entry 0 of the mantissa table (entries are
-// kTabCopies*16 bytes apart), `exp_addr` that of the exponent table.  Same values in the same order as
+// lyap_log_core (lyap_math.h) for a positive normal d, written against the two shared-memory tables, which start
+// at the beginning of the dynamic shared memory: `lane_off` is the byte offset of this lane's copy inside a
+// mantissa-table entry group ((lane & 7) * 16; groups are kTabCopies*16 bytes apart), or'ed into the bin offset so
+// that the address is one logic operation plus a constant.  Same values in the same order as
 // lyap_log_core (e*LN2HI + lp and (e-1023)*LN2LO are tabulated instead of computed), so same bits.
-__device__ __forceinline__ double log_fast(double d, unsigned tab_addr, unsigned exp_addr) {
+__device__ __forceinline__ double log_fast(double d, unsigned lane_off) {
     const unsigned hw = (unsigned)__double2hiint(d);
-    const unsigned off = (hw >> 3) & (unsigned)((LYAP_LOG_BINS - 1) * kTabCopies * 16);   // bin index * 128 bytes
-    double lp, invcb;
-    asm("ld.shared.v2.f64 {%0, %1}, [%2];" : "=d"(lp), "=d"(invcb) : "r"(tab_addr + off));
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    // bin index * 128 bytes, or'ed with this lane's copy offset (lane_off = (lane & 7) * 16)
+    const unsigned off = ((hw >> 3) & (unsigned)((LYAP_LOG_BINS - 1) * kTabCopies * 16)) | lane_off;
+    const double2 me = *reinterpret_cast<const double2*>(smem_raw + off);
+    const double lp = me.x, invcb = me.y;
     const unsigned ke = hw >> 20;
-    double khi, klo;
-    asm("ld.shared.v2.f64 {%0, %1}, [%2];" : "=d"(khi), "=d"(klo) : "r"(exp_addr + ke * 16u));
+    const double2 ee = reinterpret_cast<const double2*>(smem_raw + kTabSmemBytes)[ke];
+    const double khi = ee.x, klo = ee.y;
     // The mantissa table holds invc with 0x3FF00000 added to its high word, so subtracting d's exponent field
     // gives invc * 2^-(exponent of d): d * that == mantissa(d) * invc exactly (a power-of-two rescaling),
     // without assembling the mantissa as a separate double.
@@ -147,7 +150,7 @@ __device__ __noinline__ bool careful_steps(PixelState* ps, double rA, double rB,
 // The warp-uniform parameter choice is a select (no branch, so the block stays one scheduling region).
 template <int P, bool ACC, bool HAS_C, int U>
 __device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], const double (&rA)[P],
-                                           const double (&rB)[P], double rC, unsigned word, unsigned tab_addr, unsigned exp_addr) {
+                                           const double (&rB)[P], double rC, unsigned word, unsigned lane_off) {
     double d[U][P];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
@@ -169,7 +172,7 @@ __device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], co
 #pragma unroll
         for (int j = 0; j < U; ++j)
 #pragma unroll
-            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, exp_addr);
+            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], lane_off);
 #pragma unroll
         for (int p = 0; p < P; ++p) {
 #pragma unroll
@@ -182,7 +185,7 @@ __device__ __forceinline__ void fast_group(double (&x)[P], double (&lyap)[P], co
 // no selects, no per-step branches; every operand is fixed.
 template <int P, bool ACC, int U, unsigned PAT>
 __device__ __forceinline__ void fixed_group(double (&x)[P], double (&lyap)[P], const double (&rA)[P],
-                                            const double (&rB)[P], double rC, unsigned tab_addr, unsigned exp_addr) {
+                                            const double (&rB)[P], double rC, unsigned lane_off) {
     double d[U][P];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
@@ -202,7 +205,7 @@ __device__ __forceinline__ void fixed_group(double (&x)[P], double (&lyap)[P], c
 #pragma unroll
         for (int j = 0; j < U; ++j)
 #pragma unroll
-            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], tab_addr, exp_addr);
+            for (int p = 0; p < P; ++p) z[j][p] = log_fast(d[j][p], lane_off);
 #pragma unroll
         for (int p = 0; p < P; ++p) {
 #pragma unroll
@@ -222,11 +225,11 @@ __host__ __device__ constexpr unsigned spread_bits(unsigned m) {
 template <int P, bool ACC, bool HAS_C, int U>
 __device__ __forceinline__ void dispatch_group(double (&x)[P], double (&lyap)[P],
                                                const double (&rA)[P], const double (&rB)[P], double rC, unsigned idx,
-                                               unsigned tab_addr, unsigned exp_addr) {
+                                               unsigned lane_off) {
 #define LYAP_CASE_AB(N) \
-    case N: fixed_group<P, ACC, U, spread_bits(N)>(x, lyap, rA, rB, rC, tab_addr, exp_addr); break;
+    case N: fixed_group<P, ACC, U, spread_bits(N)>(x, lyap, rA, rB, rC, lane_off); break;
 #define LYAP_CASE_RAW(N) \
-    case N: fixed_group<P, ACC, U, N>(x, lyap, rA, rB, rC, tab_addr, exp_addr); break;
+    case N: fixed_group<P, ACC, U, N>(x, lyap, rA, rB, rC, lane_off); break;
     if (HAS_C) {
         static_assert(!HAS_C || U == 2, "three-parameter groups are two steps long");
         switch (idx) {
@@ -236,11 +239,11 @@ __device__ __forceinline__ void dispatch_group(double (&x)[P], double (&lyap)[P]
         }
     } else if (U == 2) {
         if (idx & 1u) {
-            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(3)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
-            else fixed_group<P, ACC, U, spread_bits(1)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(3)>(x, lyap, rA, rB, rC, lane_off);
+            else fixed_group<P, ACC, U, spread_bits(1)>(x, lyap, rA, rB, rC, lane_off);
         } else {
-            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(2)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
-            else fixed_group<P, ACC, U, spread_bits(0)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+            if (idx & 2u) fixed_group<P, ACC, U, spread_bits(2)>(x, lyap, rA, rB, rC, lane_off);
+            else fixed_group<P, ACC, U, spread_bits(0)>(x, lyap, rA, rB, rC, lane_off);
         }
     } else {
         switch (idx) {
@@ -267,19 +270,19 @@ __device__ __forceinline__ unsigned compress_even_bits(unsigned w) {
 // n steps of selector word `word` (2 bits per step: 0 = A, 1 = B, 2 = C).
 template <int P, bool ACC, bool HAS_C, int UNROLL>
 __device__ __forceinline__ void fast_chunk(double (&x)[P], double (&lyap)[P], const double (&rA)[P],
-                                           const double (&rB)[P], double rC, unsigned word, int n, unsigned tab_addr, unsigned exp_addr) {
+                                           const double (&rB)[P], double rC, unsigned word, int n, unsigned lane_off) {
     if (n == kStepsPerWord) {
         constexpr int U = HAS_C ? 2 : UNROLL;
         unsigned pat = HAS_C ? word : compress_even_bits(word);
         constexpr int kBits = HAS_C ? 2 * U : U;
 #pragma unroll 1
         for (int h = 0; h < kStepsPerWord / U; ++h) {
-            dispatch_group<P, ACC, HAS_C, U>(x, lyap, rA, rB, rC, pat & ((1u << kBits) - 1u), tab_addr, exp_addr);
+            dispatch_group<P, ACC, HAS_C, U>(x, lyap, rA, rB, rC, pat & ((1u << kBits) - 1u), lane_off);
             pat >>= kBits;
         }
     } else {
 #pragma unroll 1
-        for (int j = 0; j < n; ++j, word >>= 2) fast_group<P, ACC, HAS_C, 1>(x, lyap, rA, rB, rC, word, tab_addr, exp_addr);
+        for (int j = 0; j < n; ++j, word >>= 2) fast_group<P, ACC, HAS_C, 1>(x, lyap, rA, rB, rC, word, lane_off);
     }
 }
 
@@ -289,10 +292,10 @@ __device__ __forceinline__ void fast_chunk(double (&x)[P], double (&lyap)[P], co
 // straight-line block: no dispatch at all.
 template <int P, bool ACC, int KG, unsigned long long PATS, int G = 0>
 __device__ __forceinline__ void period_block(double (&x)[P], double (&lyap)[P], const double (&rA)[P], const double (&rB)[P],
-                                             double rC, unsigned tab_addr, unsigned exp_addr) {
+                                             double rC, unsigned lane_off) {
     if constexpr (G < KG) {
-        fixed_group<P, ACC, 2, (unsigned)((PATS >> (4 * G)) & 15ull)>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
-        period_block<P, ACC, KG, PATS, G + 1>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+        fixed_group<P, ACC, 2, (unsigned)((PATS >> (4 * G)) & 15ull)>(x, lyap, rA, rB, rC, lane_off);
+        period_block<P, ACC, KG, PATS, G + 1>(x, lyap, rA, rB, rC, lane_off);
     }
 }
 
@@ -313,8 +316,7 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
         tab_all[e] = t;
     }
     __syncthreads();
-    const lyap_logtab_entry* tab = tab_all + (threadIdx.x & (kTabCopies - 1));
-    const unsigned tab_addr = (unsigned)__cvta_generic_to_shared(tab);
+    const unsigned lane_off = (threadIdx.x & (kTabCopies - 1)) * 16u;
     double2* exp_tab = reinterpret_cast<double2*>(smem_raw + kTabSmemBytes);
     for (int e = threadIdx.x; e < kExpEntries; e += THREADS) {
         double2 v;
@@ -323,7 +325,6 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
         else v = make_double2(__dmul_rn((double)e, LYAP_LN2HI), __fma_rn((double)e, LYAP_LN2LO, LYAP_KLO_BIAS));
         exp_tab[e] = v;
     }
-    const unsigned exp_addr = (unsigned)__cvta_generic_to_shared(exp_tab);
 
     unsigned long long my_steps = 0;
     const long long tile_px = (long long)THREADS * P;
@@ -384,21 +385,21 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                     if (left >= CS) {             // CB whole periods, straight-line
 #pragma unroll
                         for (int b = 0; b < CB; ++b) {
-                            if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
-                            else period_block<P, false, KG, WU_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+                            if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, lane_off);
+                            else period_block<P, false, KG, WU_PATS>(x, lyap, rA, rB, rC, lane_off);
                         }
                     } else if (left >= BS) {      // the last few whole periods
 #pragma unroll 1
                         for (int b = 0; b < n / BS; ++b) {
-                            if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
-                            else period_block<P, false, KG, WU_PATS>(x, lyap, rA, rB, rC, tab_addr, exp_addr);
+                            if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, lane_off);
+                            else period_block<P, false, KG, WU_PATS>(x, lyap, rA, rB, rC, lane_off);
                         }
                     } else {                      // less than one period: one step at a time
 #pragma unroll 1
                         for (int j = s; j < nsteps; ++j) {
                             const unsigned code = (sel[(j / kStepsPerWord) % wrap] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
-                            if (acc) fast_group<P, true, HAS_C, 1>(x, lyap, rA, rB, rC, code, tab_addr, exp_addr);
-                            else fast_group<P, false, HAS_C, 1>(x, lyap, rA, rB, rC, code, tab_addr, exp_addr);
+                            if (acc) fast_group<P, true, HAS_C, 1>(x, lyap, rA, rB, rC, code, lane_off);
+                            else fast_group<P, false, HAS_C, 1>(x, lyap, rA, rB, rC, code, lane_off);
                         }
                     }
 #pragma unroll
@@ -442,8 +443,8 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                     sx[p] = x[p];
                     sl[p] = lyap[p];
                 }
-                if (acc) fast_chunk<P, true, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, tab_addr, exp_addr);
-                else fast_chunk<P, false, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, tab_addr, exp_addr);
+                if (acc) fast_chunk<P, true, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, lane_off);
+                else fast_chunk<P, false, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, lane_off);
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     if (done[p]) continue;
