@@ -135,9 +135,10 @@ int render_zoom_batch(const Options& o, const lyap_params& base) {
     std::cout << std::format(
         "{{\"frames\": {}, \"first_frame\": {}, \"width\": {}, \"height\": {}, \"sequence\": \"{}\", \"mode\": \"{}\", "
         "\"gpus\": {}, \"executed_steps\": {}, \"nominal_steps\": {}, \"ms_lambda_sum\": {:.3f}, \"ms_device_sum\": {:.3f}, "
-        "\"ms_wall\": {:.3f}, \"frames_per_s_wall\": {:.2f}, \"steps_per_s_wall\": {:.4e}}}\n",
+        "\"ms_wall\": {:.3f}, \"frames_per_s_wall\": {:.2f}, \"steps_per_s_wall\": {:.4e}, \"ms_lambda_first\": {:.3f}, "
+        "\"ms_lambda_last\": {:.3f}, \"jit_note\": \"{}\"}}\n",
         nf, o.frame, o.width, o.height, o.sequence, o.mode, devs.size(), executed, nominal, ms_lambda, ms_device, wall_ms,
-        nf / (wall_ms * 1e-3), executed / (wall_ms * 1e-3));
+        nf / (wall_ms * 1e-3), executed / (wall_ms * 1e-3), st.front().ms_lambda, st.back().ms_lambda, lyap_jit_note());
     return 0;
 }
 

@@ -26,6 +26,8 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
                                cudaStream_t st, int kind, int pixels_per_thread, int threads, size_t smem_bytes, int mode,
                                bool* launched);
 const char* jit_last_note();
+// Group-pattern period of the sequence in `a` (1..16) with the two regions' patterns, or 0 when there is none.
+int sequence_group_period(const LambdaArgs& a, unsigned long long* wu_pats, unsigned long long* acc_pats);
 
 // scratch for the min/max reduction: 2*kMinmaxBlocks doubles + one unsigned ticket (zero before first use;
 // the kernel leaves it zero again)

@@ -35,8 +35,9 @@ static cudaError_t launch_exact_variant(const LambdaArgs& a, double* out64, floa
 
 // Pixels per thread for a launch of n pixels.  Large frames: 3 (measured best on B200).  Small frames are
 // dominated by how many rounds of tiles the busiest SM runs, so the count that minimises rounds * pixels-per-thread
-// (weighted by each shape's measured per-pixel cost) is taken.  LYAP_EXACT_VARIANT=0..4 overrides (tuning knob).
-static int exact_pixels_per_thread(long long n_pixels, int sm_count, int* threads) {
+// (weighted by each shape's measured per-pixel cost) is taken; `spec` says that the 2- and 3-pixel shapes can run as
+// instances compiled for the sequence, which are faster.  LYAP_EXACT_VARIANT=0..4 overrides (tuning knob).
+static int exact_pixels_per_thread(long long n_pixels, int sm_count, int* threads, bool spec) {
     static const int env = [] {
         const char* e = getenv("LYAP_EXACT_VARIANT");
         return e ? atoi(e) : -1;
@@ -50,7 +51,7 @@ static int exact_pixels_per_thread(long long n_pixels, int sm_count, int* thread
         default: break;
     }
     const int cand[3] = {3, 2, 4};
-    const double cost[3] = {1.0, 1.035, 1.015};
+    const double cost[3] = {spec ? 0.92 : 1.0, spec ? 0.95 : 1.035, 1.015};
     int best = 3;
     double best_t = 1e300;
     for (int i = 0; i < 3; ++i) {
@@ -74,12 +75,14 @@ cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32
     (has_c ? launch_exact_variant<P, T, true, U>(a, out64, out32, steps, sm_count, st)            \
            : launch_exact_variant<P, T, false, U>(a, out64, out32, steps, sm_count, st))
     int threads = 512;
-    const int ppt = exact_pixels_per_thread(a.n_pixels, sm_count, &threads);
     // a periodic sequence can run an instance of this kernel compiled for its patterns (LYAP_JIT=0 turns that off,
     // 2 compiles at once instead of after some work has been seen)
+    const char* je = getenv("LYAP_JIT");
+    const int jit_mode = je ? atoi(je) : 1;
+    unsigned long long wu_pats = 0, acc_pats = 0;
+    const bool spec = jit_mode > 0 && sequence_group_period(a, &wu_pats, &acc_pats) > 0;
+    const int ppt = exact_pixels_per_thread(a.n_pixels, sm_count, &threads, spec);
     if (threads == 512 && ppt <= 3) {   // with 4 pixels per thread the specialised instance measured slower
-        const char* je = getenv("LYAP_JIT");
-        const int jit_mode = je ? atoi(je) : 1;
         bool launched = false;
         const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, 0, ppt, 512, kExactSmemBytes, jit_mode,
                                                  &launched);
