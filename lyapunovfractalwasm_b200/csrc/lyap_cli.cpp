@@ -224,17 +224,12 @@ int main(int argc, char** argv) {
         return 1;
     }
     if (!o.out.empty()) {
-        std::ofstream f(o.out, std::ios::binary);
-        if (!f) { std::cerr << "lyap_cli: cannot write " << o.out << "\n"; return 1; }
-        if (o.out.ends_with(".ppm")) {
-            f << std::format("P6\n{} {}\n255\n", o.width, o.height);
-            std::vector<uint8_t> rgb(n * 3);
-            for (size_t i = 0; i < n; ++i) { rgb[3 * i] = rgba[4 * i]; rgb[3 * i + 1] = rgba[4 * i + 1]; rgb[3 * i + 2] = rgba[4 * i + 2]; }
-            f.write(reinterpret_cast<const char*>(rgb.data()), static_cast<std::streamsize>(rgb.size()));
-        } else if (want_f64) {
+        if (want_f64) {
+            std::ofstream f(o.out, std::ios::binary);
+            if (!f) { std::cerr << "lyap_cli: cannot write " << o.out << "\n"; return 1; }
             f.write(reinterpret_cast<const char*>(norm.data()), static_cast<std::streamsize>(n * 8));
         } else {
-            f.write(reinterpret_cast<const char*>(rgba.data()), static_cast<std::streamsize>(rgba.size()));
+            write_frame(o.out, rgba.data(), o.width, o.height);
         }
     }
     std::cout << std::format(
