@@ -193,6 +193,7 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # whatever NCCL logs must not land beside the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     eng = L.Engine(local_rank)
