@@ -184,6 +184,11 @@ def main():
         reference_arm(args, rank, world)
         return
 
+    # stdout carries exactly one JSON line: anything a library prints there (NCCL's version banner, ...) goes to stderr
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     import numpy as np
     import torch
     import lyapunovfractalwasm_b200 as L
@@ -193,7 +198,6 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # whatever NCCL logs must not land beside the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     eng = L.Engine(local_rank)
@@ -420,7 +424,8 @@ def main():
             line["e2e_batch"] = e2e_batch
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_leg()
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
