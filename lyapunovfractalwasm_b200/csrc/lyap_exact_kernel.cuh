@@ -365,8 +365,9 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
             const int word0 = acc ? a.acc_word0 : 0;
             const int wrap = acc ? a.acc_wrap : a.wu_wrap;
             if constexpr (KG > 0) {
-                // specialised walk: chunks of CB whole periods (>= 16 steps), then the generic step for the rest
-                constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, CS = CB * BS;
+                // specialised walk: chunks of REP blocks of CB whole periods (>= 16 steps each), then one block, whole periods, single steps
+                // REP = 2 blocks between exit tests measured best (1: more tests and state copies; 3 and more: slower code)
+                constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, REP = 2, CS = CB * BS * REP;
                 const unsigned* sel = a.sel + word0;
                 int s = 0;
                 while (s < nsteps) {
@@ -375,14 +376,23 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                     for (int p = 0; p < P; ++p) all_done = all_done && done[p];
                     if (__all_sync(0xFFFFFFFFu, all_done)) break;
                     const int left = nsteps - s;
-                    const int n = left >= CS ? CS : (left >= BS ? left / BS * BS : left);
+                    const int n = left >= CS ? CS : (left >= CB * BS ? CB * BS : (left >= BS ? left / BS * BS : left));
                     double sx[P], sl[P];
 #pragma unroll
                     for (int p = 0; p < P; ++p) {
                         sx[p] = x[p];
                         sl[p] = lyap[p];
                     }
-                    if (left >= CS) {             // CB whole periods, straight-line
+                    if (left >= CS) {             // CB whole periods, straight-line, REP times
+#pragma unroll 1
+                        for (int rep = 0; rep < REP; ++rep) {
+#pragma unroll
+                            for (int b = 0; b < CB; ++b) {
+                                if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, lane_off);
+                                else period_block<P, false, KG, WU_PATS>(x, lyap, rA, rB, rC, lane_off);
+                            }
+                        }
+                    } else if (left >= CB * BS) { // one straight-line block
 #pragma unroll
                         for (int b = 0; b < CB; ++b) {
                             if (acc) period_block<P, true, KG, ACC_PATS>(x, lyap, rA, rB, rC, lane_off);
