@@ -740,8 +740,9 @@ struct FrameSmall {
 // One set of device buffers; a worker alternates between two, so that one frame's copies to the host run
 // while the next frame is computed.
 struct FrameSlot {
+    void* block = nullptr;           // one device allocation: lambda | normalised | RGBA | min/max + step counter
     void *lam = nullptr, *norm = nullptr, *rgba = nullptr, *small = nullptr;
-    FrameSmall* h_small = nullptr;   // pinned
+    FrameSmall* h_small = nullptr;   // pinned, owned by the caller of the workers
     cudaEvent_t begun = nullptr, lambda_done = nullptr, computed = nullptr, copied = nullptr;
     int frame = -1;
 };
@@ -749,7 +750,7 @@ struct FrameSlot {
 // Frames first, first + stride, ... on one device: kernels in order on the context's stream, copies on a second
 // stream behind an event, two buffer sets.
 void frames_worker(FramesShared& sh, int device, int first, int stride, const lyap_params* frames, int n_frames,
-                   double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats) {
+                   double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats, FrameSmall* pinned) {
     lyap_ctx* c = nullptr;
     if (lyap_create(&c, device) != LYAP_OK) return frames_fail(sh, LYAP_ERR_CUDA, lyap_last_error());
     cudaStream_t copy = nullptr;
@@ -764,9 +765,7 @@ void frames_worker(FramesShared& sh, int device, int first, int stride, const ly
         cudaStreamSynchronize(c->stream);
         if (copy) cudaStreamSynchronize(copy);
         for (FrameSlot& s : slots) {
-            for (void* q : {s.lam, s.norm, s.rgba, s.small})
-                if (q) cudaFree(q);
-            if (s.h_small) cudaFreeHost(s.h_small);
+            if (s.block) cudaFree(s.block);
             for (cudaEvent_t e : {s.begun, s.lambda_done, s.computed, s.copied})
                 if (e) cudaEventDestroy(e);
         }
@@ -784,12 +783,18 @@ void frames_worker(FramesShared& sh, int device, int first, int stride, const ly
         if (fr_e != cudaSuccess) return bail_cuda(fr_e, #call);    \
     } while (0)
     FR(cudaStreamCreateWithFlags(&copy, cudaStreamNonBlocking));
-    for (FrameSlot& s : slots) {
-        FR(cudaMalloc(&s.lam, max_px * 8));
-        FR(cudaMalloc(&s.norm, max_px * 8));
-        if (any_rgba) FR(cudaMalloc(&s.rgba, max_px * 4));
-        FR(cudaMalloc(&s.small, 32));
-        FR(cudaMallocHost(reinterpret_cast<void**>(&s.h_small), sizeof(FrameSmall)));
+    // allocations are few on purpose: with several devices in one process every cudaMalloc / cudaFree and, far more,
+    // every pinned allocation is serialised across the workers
+    const size_t px8 = (max_px * 8 + 255) / 256 * 256, px4 = any_rgba ? (max_px * 4 + 255) / 256 * 256 : 0;
+    for (int i = 0; i < 2; ++i) {
+        FrameSlot& s = slots[i];
+        FR(cudaMalloc(&s.block, 2 * px8 + px4 + 256));
+        char* base = static_cast<char*>(s.block);
+        s.lam = base;
+        s.norm = base + px8;
+        s.rgba = any_rgba ? base + 2 * px8 : nullptr;
+        s.small = base + 2 * px8 + px4;
+        s.h_small = pinned + i;
         for (cudaEvent_t* e : {&s.begun, &s.lambda_done, &s.computed, &s.copied}) FR(cudaEventCreate(e));
     }
     // the slot's frame has reached the host: fill in its statistics
@@ -869,12 +874,21 @@ extern "C" int lyap_render_frames(const lyap_params* frames, int32_t n_frames, i
         if (g.rows != frames[k].height)
             return fail(LYAP_ERR_INVALID, "lyap_render_frames renders whole frames (row_begin = row_end = 0)");
     }
+    if (n_frames == 0) return LYAP_OK;
+    // one pinned block for every worker's two small read-back records
+    int n_dev_present = 0;
+    CU(cudaGetDeviceCount(&n_dev_present));
+    if (devices[0] < 0 || devices[0] >= n_dev_present) return fail(LYAP_ERR_INVALID, "no such device");
+    CU(cudaSetDevice(devices[0]));
+    FrameSmall* pinned = nullptr;
+    CU(cudaMallocHost(reinterpret_cast<void**>(&pinned), (size_t)n_devices * 2 * sizeof(FrameSmall)));
     FramesShared sh;
     std::vector<std::thread> workers;
     for (int r = 0; r < n_devices && r < n_frames; ++r)
         workers.emplace_back(frames_worker, std::ref(sh), (int)devices[r], r, (int)n_devices, frames, (int)n_frames, out_norm,
-                             out_rgba, stats);
+                             out_rgba, stats, pinned + 2 * r);
     for (auto& w : workers) w.join();
+    cudaFreeHost(pinned);
     if (sh.status != LYAP_OK) return fail(sh.status, sh.error);
     return LYAP_OK;
 }
