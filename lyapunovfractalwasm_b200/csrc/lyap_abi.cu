@@ -593,10 +593,11 @@ void multi_worker(MultiShared& sh, const lyap_params& base, int device, long lon
     const long long H = base.height, W = base.width;
     const int above = b0 > 0 ? 1 : 0, below = b1 < H ? 1 : 0;
     const long long rows_all = (b1 - b0) + above + below, rows_own = b1 - b0;
-    void *d_lam = nullptr, *d_norm = nullptr, *d_rgba = nullptr, *d_small = nullptr;
+    // one device allocation for the band: lambda | normalised | RGBA | min/max + step counter (allocations are
+    // serialised across the workers of a process, so they are kept few)
+    void *block = nullptr, *d_lam = nullptr, *d_norm = nullptr, *d_rgba = nullptr, *d_small = nullptr;
     auto cleanup = [&]() {
-        for (void* q : {d_lam, d_norm, d_rgba, d_small})
-            if (q) lyap_device_free(c, q);
+        if (block) lyap_device_free(c, block);
         lyap_destroy(c);
     };
     auto bail = [&](int st) {
@@ -604,11 +605,15 @@ void multi_worker(MultiShared& sh, const lyap_params& base, int device, long lon
         cleanup();
     };
     const bool colour = out_norm || out_rgba;
-    int st = lyap_device_alloc(c, &d_lam, (size_t)rows_all * W * 8);
-    if (st == LYAP_OK) st = lyap_device_alloc(c, &d_small, 32);
-    if (st == LYAP_OK && colour) st = lyap_device_alloc(c, &d_norm, (size_t)rows_all * W * 8);
-    if (st == LYAP_OK && out_rgba) st = lyap_device_alloc(c, &d_rgba, (size_t)rows_own * W * 4);
+    const size_t lam_bytes = ((size_t)rows_all * W * 8 + 255) / 256 * 256;
+    const size_t norm_bytes = colour ? lam_bytes : 0;
+    const size_t rgba_bytes = out_rgba ? ((size_t)rows_own * W * 4 + 255) / 256 * 256 : 0;
+    int st = lyap_device_alloc(c, &block, lam_bytes + norm_bytes + rgba_bytes + 256);
     if (st != LYAP_OK) return bail(st);
+    d_lam = block;
+    d_norm = colour ? static_cast<char*>(block) + lam_bytes : nullptr;
+    d_rgba = out_rgba ? static_cast<char*>(block) + lam_bytes + norm_bytes : nullptr;
+    d_small = static_cast<char*>(block) + lam_bytes + norm_bytes + rgba_bytes;
     double* d_mm = static_cast<double*>(d_small);
     uint64_t* d_steps = reinterpret_cast<uint64_t*>(d_mm + 2);
     uint64_t zero = 0;
