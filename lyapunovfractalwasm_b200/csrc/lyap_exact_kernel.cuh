@@ -437,24 +437,31 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                 }
                 continue;
             }
-            const int nchunks = nsteps / kStepsPerWord + (nsteps % kStepsPerWord != 0);
-            for (int c = 0, wi = 0; c < nchunks; ++c) {
+            // generic walk: the selector words one after the other, exit tests after every second full word
+            const unsigned* sel = a.sel + word0;
+            int s = 0, wi = 0;
+            while (s < nsteps) {
                 bool all_done = true;
 #pragma unroll
                 for (int p = 0; p < P; ++p) all_done = all_done && done[p];
                 if (__all_sync(0xFFFFFFFFu, all_done)) break;
 
-                const unsigned word = a.sel[word0 + wi];
-                if (++wi == wrap) wi = 0;
-                const int n = min(kStepsPerWord, nsteps - c * kStepsPerWord);
+                const int left = nsteps - s;
+                const int n = left >= 2 * kStepsPerWord ? 2 * kStepsPerWord : (left >= kStepsPerWord ? kStepsPerWord : left);
                 double sx[P], sl[P];
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     sx[p] = x[p];
                     sl[p] = lyap[p];
                 }
-                if (acc) fast_chunk<P, true, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, lane_off);
-                else fast_chunk<P, false, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, n, lane_off);
+#pragma unroll 1
+                for (int k = 0; k < n; k += kStepsPerWord) {
+                    const unsigned word = sel[wi];
+                    if (++wi == wrap) wi = 0;
+                    const int m = min(kStepsPerWord, n - k);
+                    if (acc) fast_chunk<P, true, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, m, lane_off);
+                    else fast_chunk<P, false, HAS_C, UNROLL>(x, lyap, rA, rB, rC, word, m, lane_off);
+                }
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     if (done[p]) continue;
@@ -465,8 +472,8 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                         my_steps += (unsigned long long)n;
                     } else {
                         PixelState ps{sx[p], sl[p], valid[p]};
-                        const bool dead = acc ? careful_chunk<true>(&ps, rA[p], rB[p], rC, word, n, &my_steps)
-                                              : careful_chunk<false>(&ps, rA[p], rB[p], rC, word, n, &my_steps);
+                        const bool dead = acc ? careful_steps<true>(&ps, rA[p], rB[p], rC, sel, wrap, s, n, &my_steps)
+                                              : careful_steps<false>(&ps, rA[p], rB[p], rC, sel, wrap, s, n, &my_steps);
                         x[p] = ps.x;
                         lyap[p] = ps.lyap;
                         valid[p] = ps.valid;
@@ -477,6 +484,7 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
                         }
                     }
                 }
+                s += n;
             }
         }
 
