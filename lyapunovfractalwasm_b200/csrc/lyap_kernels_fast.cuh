@@ -213,7 +213,9 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
             const int word0 = acc ? a.acc_word0 : 0;
             const int wrap = acc ? a.acc_wrap : a.wu_wrap;
             if constexpr (KG > 0) {
-                constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, CS = CB * BS;
+                // exit tests after REP straight-line blocks of CB whole periods (measured: 1 -> 4 blocks saves 12 % (fp64) and
+                // 16 % (fp32) of a large frame's time, 8 another 2 %; a pixel that leaves (0,1) replays at most one such chunk)
+                constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, REP = 4, CS = CB * BS * REP;
                 const unsigned* sel = a.sel + word0;
                 int s = 0;
                 while (s < nsteps) {
@@ -222,7 +224,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                     for (int p = 0; p < P; ++p) all_done = all_done && done[p];
                     if (__all_sync(0xFFFFFFFFu, all_done)) break;
                     const int left = nsteps - s;
-                    const int n = left >= CS ? CS : (left >= BS ? left / BS * BS : left);
+                    const int n = left >= CS ? CS : (left >= CB * BS ? CB * BS : (left >= BS ? left / BS * BS : left));
                     T sx[P], sp[P];
                     int se[P], emin[P], emax[P];
 #pragma unroll
@@ -234,6 +236,12 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                         emax[p] = 0;
                     }
                     if (left >= CS) {
+#pragma unroll 1
+                        for (int rep = 0; rep < REP; ++rep) {
+                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                            else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                        }
+                    } else if (left >= CB * BS) {
                         if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
                         else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
                     } else if (left >= BS) {
