@@ -25,12 +25,12 @@ __device__ const lyap_logtab_entry g_lyap_logtab[LYAP_LOG_BINS] = {LYAP_LOG_TABL
 // quarter warp, whose 8 lanes then hit 8 different 16-byte bank groups whatever their indices are,
 // so the lookups never conflict.
 //
-// Steps run in chunks of up to 16 without per-step exit tests.  That is sound because leaving (0,1)
+// Steps run in chunks of 16 to about 40 without per-step exit tests.  That is sound because leaving (0,1)
 // is permanent for x <- r x (1-x) with r > 0 (x >= 1 gives x <= 0 next, x <= 0 stays <= 0, NaN stays
 // NaN), so testing x after the chunk finds every exit, and the only other irregular event, a zero
 // derivative (x == 0.5 exactly, skipped and not counted by the reference, :71-74), has exponent field 0,
 // for which the exponent table holds -inf: the running sum turns non-finite.  A chunk in which anything irregular
-// happened is rolled back and redone by `careful_chunk`, which follows the reference step by step.
+// happened is rolled back and redone by `careful_chunk` / `careful_steps`, which follow the reference step by step.
 // ---------------------------------------------------------------------------------------------
 
 constexpr int kTabCopies = 8;
