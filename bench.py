@@ -407,8 +407,8 @@ def main():
             "instr_per_step": {"warmup": OPS_WARM, "accumulated": OPS_ACC} if mode == L.MODE_EXACT else FAST_OPS,
             "ms_per_launch": ms_lambda,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch on the 4096x4096 frame (ncu, profiles/):
-            # 2.3 MB read + 76.9 MB written; less than the 134 MB of stores because the tail is still in L2 at kernel end
-            "traffic": 79.2e6 * rows_all / 4096 if mode == L.MODE_EXACT and not strong else None,
+            # 1.9 MB read + 76.1 MB written; less than the 134 MB of stores because the tail is still in L2 at kernel end
+            "traffic": 78.0e6 * rows_all / 4096 if mode == L.MODE_EXACT and not strong else None,
             "hbm": {"algorithmic_bytes_per_launch": out_bytes, "store_gbs": out_bytes / (ms_lambda * 1e-3) / 1e9,
                     "peak_gbs": hbm_peak, "peak_source": "MEASURED_PEAKS.json (measured)" if hbm_peak else "absent"},
         }
