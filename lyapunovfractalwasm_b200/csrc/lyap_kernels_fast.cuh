@@ -5,7 +5,7 @@
 // arithmetic is rearranged for speed and is NOT bit-compatible with the reference:
 //   t = r*x;  deriv = fma(-2,t,r) = r(1-2x);  x' = fma(-t,x,t) = r x (1-x)         (4 fused ops/step)
 // and instead of one log per step the |deriv| are multiplied together; the product's exponent is
-// moved into an integer every 16 (fp64) or 4 (fp32) steps, and one log of the remaining mantissa is
+// moved into an integer every 16 (fp64) or 12 (fp32) steps, and one log of the remaining mantissa is
 // taken per pixel at the end:  sum log|deriv| = E*ln2 + log(mantissa product).
 // A chunk in which the orbit left (0,1) or a derivative was exactly zero is rolled back and redone
 // step by step with the reference's rules (skip zero terms, stop at the exit, keep the partial sum).
@@ -34,7 +34,10 @@ struct FastTraits<double> {
 
 template <>
 struct FastTraits<float> {
-    static constexpr int kRenorm = 4;
+    // A product that is subnormal or zero when it is stripped sends the chunk to the step-by-step path.  Falling below
+    // 2^-126 from [1,2) takes five or more consecutive derivatives near 2^-25 (x within a few ulps of 0.5 each time);
+    // only a product that did so and was multiplied back above 2^-126 before the strip would lose low bits unnoticed.
+    static constexpr int kRenorm = 12;
     static __device__ __forceinline__ float fma_(float a, float b, float c) { return __fmaf_rn(a, b, c); }
     static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
     static __device__ __forceinline__ float abs_(float a) { return fabsf(a); }
