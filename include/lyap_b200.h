@@ -38,8 +38,8 @@ enum lyap_status {
 
 enum lyap_mode {
     LYAP_MODE_EXACT = 0,       /* fp64, reference operation order, one log per step: bit-exact */
-    LYAP_MODE_FAST_FP64 = 1,   /* fp64 FMA orbit, product of derivatives, one log per 16 steps */
-    LYAP_MODE_FAST_FP32 = 2    /* fp32 orbit and products, fp64 exponent sum */
+    LYAP_MODE_FAST_FP64 = 1,   /* fp64 FMA orbit, running product of derivatives, one log per pixel */
+    LYAP_MODE_FAST_FP32 = 2    /* fp32 orbit and products, integer exponent sum, one log per pixel */
 };
 
 enum lyap_palette {            /* web/fractal_renderer.js:207-281; unknown names mean cosmic (:280) */
