@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define LYAP_ABI_VERSION 1
+#define LYAP_ABI_VERSION 2
 
 enum lyap_status {
     LYAP_OK = 0,
@@ -41,6 +41,7 @@ enum lyap_mode {
     LYAP_MODE_FAST_FP64 = 1,   /* fp64 FMA orbit, running product of derivatives, one log per pixel */
     LYAP_MODE_FAST_FP32 = 2    /* fp32 orbit and products, integer exponent sum, one log per pixel */
 };
+/* The fast modes accept at most 2^24 steps per pixel (warmup + iterations): LYAP_ERR_TOO_LARGE beyond. */
 
 enum lyap_palette {            /* web/fractal_renderer.js:207-281; unknown names mean cosmic (:280) */
     LYAP_PALETTE_COSMIC = 0,
@@ -165,27 +166,75 @@ int lyap_glow(lyap_ctx* ctx, const uint8_t* rgba_in, int32_t width, int32_t heig
 int lyap_render(lyap_ctx* ctx, const lyap_params* p, double* out_lambda, float* out_lambda32, double* out_norm,
                 uint8_t* out_rgba, lyap_progress_fn progress, lyap_render_stats* stats);
 
-/* One frame over several devices of this machine, from one process (one worker thread and one context per
- * entry of `devices`; the same ordinal may appear more than once).  Rows are split into contiguous bands
- * (reference rows loop, src/lyapunov_fractal.hpp:41); each band recomputes one halo row per inner side for the
- * 3x3 mean; the only exchange is the frame's min/max (normalizeData, :110-125), done on the host.  Every band
- * is copied into its place in the host buffers (any may be NULL), so the result is byte-identical to
- * lyap_render on one device.  If a worker does not reach the exchange within timeout_seconds (<= 0: 60 s) the
- * call returns LYAP_ERR_TIMEOUT once the workers that did arrive have stopped; a negative ordinal in
- * `devices` stands for a worker that never arrives (used by the tests to exercise that path without
- * disturbing a GPU).  stats->ms_total_device is the wall-clock time of the whole call here. */
-int lyap_render_multi(const lyap_params* p, int32_t n_devices, const int32_t* devices, double* out_lambda,
-                      double* out_norm, uint8_t* out_rgba, double timeout_seconds, lyap_render_stats* stats);
+/* ---- several devices of this machine, from one process ---- */
+
+/* A set of devices kept ready for frames split into row bands and for batches of whole frames: per device one
+ * engine context, two streams, its buffers (grown on demand, kept between calls) and a pinned read-back record;
+ * with use_nccl != 0 also one NCCL communicator per device (ncclCommInitAll; the NCCL library is looked up with
+ * dlopen("libnccl.so.2"), path override: environment LYAP_NCCL_PATH).  The same ordinal may be listed more than
+ * once and a negative ordinal stands for a band whose worker never arrives (the tests use it to exercise the
+ * deadline without disturbing a GPU); in both cases, and when the library is missing or its set-up fails, the object
+ * works without NCCL (min/max through the host, gather by peer copies) and lyap_multi_note() says why.
+ * One call at a time per object. */
+typedef struct lyap_multi lyap_multi;
+int lyap_multi_create(lyap_multi** m, int32_t n_devices, const int32_t* devices, int32_t use_nccl);
+int lyap_multi_destroy(lyap_multi* m);
+/* "" while NCCL is in use (or was not asked for), otherwise the reason it is not. */
+const char* lyap_multi_note(lyap_multi* m);
+
+enum lyap_multi_flags {
+    LYAP_MULTI_GATHER_RGBA = 1,      /* collect every band's RGBA8 in the first device's own frame buffer */
+    LYAP_MULTI_GATHER_LAMBDA32 = 2,  /* likewise the (float)lambda bands */
+    LYAP_MULTI_HOST_EXCHANGE = 4     /* frame min/max through the host even when NCCL is available */
+};
+
+typedef struct lyap_multi_stats {
+    uint64_t executed_steps, nominal_steps;
+    double lambda_min, lambda_max;
+    float ms_wall;                 /* the whole call, host clock */
+    float ms_lambda_max;           /* slowest band: its lambda kernels (CUDA events on its stream) */
+    float ms_device_max;           /* slowest band: lambda ... RGBA */
+    float ms_gather;               /* first device: gather posted ... last byte in its frame buffer (CUDA events) */
+    uint64_t gather_bytes;         /* bytes that came from the other devices */
+    int32_t kernel_launches;       /* this library's kernels, all devices */
+    int32_t used_nccl;             /* 1: all-reduce / send / recv went through NCCL; 0: host exchange, peer copies */
+} lyap_multi_stats;
+
+/* One frame as contiguous row bands, one per listed device (the reference's rows loop, src/lyapunov_fractal.hpp:41,
+ * and its result vector, :28,84,101).  Each band recomputes one halo row per inner side for the page's 3x3 mean; the
+ * one exchange is the frame's min/max (normalizeData, :110-125): a single all-reduce(MIN) of (min, -max).
+ * Host outputs (any may be NULL) receive every band in its place, so the bytes equal lyap_render's on one device.
+ * With a GATHER flag the bands are first sent to the first listed device -- ncclSend on each other device, the
+ * matching ncclRecvs posted as one group on the first; peer copies without NCCL -- into ONE contiguous frame in that
+ * device's memory (lyap_multi_gathered), and out_rgba / out_lambda32, if given, are copied from there.  The gather is
+ * posted only after every band has finished, and is timed on its own (stats->ms_gather).
+ * Failure handling: every step that needs all bands is preceded by a host-side rendezvous with the deadline
+ * (timeout_seconds, <= 0: 60 s), so a band that fails or never arrives gives its error / LYAP_ERR_TIMEOUT before
+ * any collective is enqueued; afterwards completion is polled (stream state, ncclCommGetAsyncError) against the same
+ * deadline, and on expiry or an NCCL error the communicators are aborted: LYAP_ERR_TIMEOUT / LYAP_ERR_COMM. */
+int lyap_multi_render(lyap_multi* m, const lyap_params* p, int32_t flags, double* out_lambda, float* out_lambda32,
+                      double* out_norm, uint8_t* out_rgba, double timeout_seconds, lyap_multi_stats* stats);
+
+/* Device pointers (first listed device) of the frames the last GATHER render filled; valid until the next render that
+ * needs a larger one, or lyap_multi_destroy.  NULL for a kind never gathered. */
+int lyap_multi_gathered(lyap_multi* m, uint8_t** d_rgba, float** d_lambda32);
 
 /* A batch of independent whole frames -- a zoom sequence: each frame its own window, hence its own min/max
  * (the page calls computeLyapunovFractal once per view, web/fractal_renderer.js:132-154) -- dealt round-robin to
- * the listed devices: frame k goes to devices[k % n_devices].  One worker thread and one context per device;
- * on each device the kernels of successive frames run back to back on one stream while the previous frame's
- * outputs are copied to the host on a second stream from a second set of buffers, so copies cost no device time
- * as long as they are shorter than a frame.  out_norm / out_rgba are arrays of n_frames host pointers (either
- * array, or single entries, may be NULL; pinned memory from lyap_host_alloc copies fastest); stats, if given,
- * is an array of n_frames records (ms_copies = time from the frame's last kernel to its last byte on the host).
- * Every frame's bytes equal those of lyap_render on that frame. */
+ * the object's devices: frame k goes to device k % n.  On each device the kernels of successive frames run back to
+ * back on one stream while the previous frame's outputs are copied to the host on a second stream from a second set
+ * of buffers, so copies cost no device time as long as they are shorter than a frame.  out_norm / out_rgba are arrays
+ * of n_frames host pointers (either array, or single entries, may be NULL; pinned memory from lyap_host_alloc copies
+ * fastest); stats, if given, is an array of n_frames records (ms_copies = time from the frame's last kernel to its
+ * last byte on the host).  Every frame's bytes equal those of lyap_render on that frame. */
+int lyap_multi_render_frames(lyap_multi* m, const lyap_params* frames, int32_t n_frames, double* const* out_norm,
+                             uint8_t* const* out_rgba, lyap_render_stats* stats);
+
+/* One-call forms: a temporary lyap_multi (without NCCL) around one lyap_multi_render (host min/max exchange, no
+ * gather) / lyap_multi_render_frames.  They pay for contexts and buffers on every call; keep a lyap_multi for
+ * repeated use.  stats->ms_total_device of lyap_render_multi is the wall-clock time of the render inside. */
+int lyap_render_multi(const lyap_params* p, int32_t n_devices, const int32_t* devices, double* out_lambda,
+                      double* out_norm, uint8_t* out_rgba, double timeout_seconds, lyap_render_stats* stats);
 int lyap_render_frames(const lyap_params* frames, int32_t n_frames, int32_t n_devices, const int32_t* devices,
                        double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats);
 
@@ -203,15 +252,23 @@ int lyap_render_frames(const lyap_params* frames, int32_t n_frames, int32_t n_de
  *     outside any stream capture.
  *   - All calls on a device share the one array: calls that may overlap on the GPU (different streams,
  *     different threads) race and give wrong results; order them on one stream or with events.
- *   - d_values / d_minmax are device pointers supplied by the caller; only enqueues work. */
+ *   - d_values / d_minmax are device pointers supplied by the caller; only enqueues work.
+ *   - The looked-up addresses are kept in a fixed table of LYAP_NOALLOC_MAX_DEVICES entries (no host allocation
+ *     either): on a device whose ordinal is that or larger the call returns LYAP_ERR_INVALID. */
 #define LYAP_NOALLOC_MAX_VALUES (1ull << 32)
+#define LYAP_NOALLOC_MAX_DEVICES 64
 int lyap_minmax_device_noalloc(const double* d_values, uint64_t n, double* d_minmax, void* cuda_stream);
 
-/* No counterpart in the reference.  For a periodic sequence the exact lambda kernel may run as an instance compiled
- * at run time for that sequence's A/B(/C) patterns (same source, same bits, no per-step choice left); environment
- * LYAP_JIT=0 disables that, 2 compiles on first use instead of after about 2e10 steps of work with the sequence.
- * Returns why the last attempt to build or use such an instance fell back to the precompiled kernel ("" if none did). */
+/* No counterpart in the reference.  For a periodic sequence the lambda kernels run as an instance made for that
+ * sequence's A/B(/C) patterns (same source, same bits, no per-step choice left): one compiled with the library for
+ * the patterns of "AB", "AABAB", "BBBBBBAAAAAA" (500 warm-up steps), "ABC" with a third parameter and "ABB", else one
+ * compiled at run time (NVRTC) once about 2e10 steps of work with the sequence have been asked for.  Environment:
+ * LYAP_JIT=0 never compiles at run time, 2 compiles on first use; LYAP_PREBUILT=0 ignores the library's own instances
+ * (both 0: the generic kernels, which choose the pattern every two steps).
+ * lyap_jit_note: why the last attempt to build or use a run-time instance fell back ("" if none did).
+ * lyap_last_kernel: which lambda kernel the calling thread's last launch used, and how it was made. */
 const char* lyap_jit_note(void);
+const char* lyap_last_kernel(void);
 
 /* No counterpart in the reference (host only, needs no GPU).  Writes to *code which parameter step `step` of the
  * warm-up (region 0) or of the accumulation (region 1) uses under `params` -- 0 = column parameter ('A'),

@@ -49,6 +49,20 @@ class RenderStats(ctypes.Structure):
     ]
 
 
+class MultiStats(ctypes.Structure):
+    """struct lyap_multi_stats."""
+    _fields_ = [
+        ("executed_steps", ctypes.c_uint64), ("nominal_steps", ctypes.c_uint64),
+        ("lambda_min", ctypes.c_double), ("lambda_max", ctypes.c_double),
+        ("ms_wall", ctypes.c_float), ("ms_lambda_max", ctypes.c_float), ("ms_device_max", ctypes.c_float),
+        ("ms_gather", ctypes.c_float), ("gather_bytes", ctypes.c_uint64),
+        ("kernel_launches", ctypes.c_int32), ("used_nccl", ctypes.c_int32),
+    ]
+
+
+MULTI_GATHER_RGBA, MULTI_GATHER_LAMBDA32, MULTI_HOST_EXCHANGE = 1, 2, 4
+
+
 class LyapError(RuntimeError):
     def __init__(self, status, message):
         super().__init__("lyap status %d: %s" % (status, message))
@@ -62,6 +76,15 @@ ABI = {
     "lyap_self_test": (ctypes.c_int, []),
     "lyap_last_error": (ctypes.c_char_p, []),
     "lyap_jit_note": (ctypes.c_char_p, []),
+    "lyap_last_kernel": (ctypes.c_char_p, []),
+    "lyap_multi_create": (ctypes.c_int, [ctypes.POINTER(_P), ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
+    "lyap_multi_destroy": (ctypes.c_int, [_P]),
+    "lyap_multi_note": (ctypes.c_char_p, [_P]),
+    "lyap_multi_render": (ctypes.c_int, [_P, ctypes.POINTER(LyapParams), ctypes.c_int32, _P, _P, _P, _P, ctypes.c_double,
+                                         ctypes.POINTER(MultiStats)]),
+    "lyap_multi_gathered": (ctypes.c_int, [_P, ctypes.POINTER(_P), ctypes.POINTER(_P)]),
+    "lyap_multi_render_frames": (ctypes.c_int, [_P, ctypes.POINTER(LyapParams), ctypes.c_int32, ctypes.POINTER(_P),
+                                                ctypes.POINTER(_P), ctypes.POINTER(RenderStats)]),
     "lyap_selector_code": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.c_int, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)]),
     "lyap_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "lyap_params_default": (None, [ctypes.POINTER(LyapParams)]),
@@ -210,6 +233,67 @@ def render_multi(params, devices, want=("lambda", "norm", "rgba"), timeout_secon
                                             ptrs["rgba"], timeout_seconds, ctypes.byref(stats)))
     out["stats"] = stats
     return out
+
+
+class Multi:
+    """lyap_multi: a set of devices kept ready for banded frames and frame batches (see include/lyap_b200.h)."""
+
+    def __init__(self, devices, use_nccl=False):
+        self.lib = load_library()
+        self.devices = list(devices)
+        devs = (ctypes.c_int32 * len(self.devices))(*self.devices)
+        m = ctypes.c_void_p()
+        _check(self.lib.lyap_multi_create(ctypes.byref(m), len(self.devices), devs, 1 if use_nccl else 0))
+        self.m = m
+
+    def note(self):
+        return self.lib.lyap_multi_note(self.m).decode()
+
+    def close(self):
+        if self.m:
+            self.lib.lyap_multi_destroy(self.m)
+            self.m = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def render(self, params, want=("lambda", "norm", "rgba"), flags=0, timeout_seconds=0.0):
+        """lyap_multi_render into fresh numpy arrays (+ 'stats')."""
+        h, w = params.height, params.width
+        out, ptrs = {}, {}
+        for key, dtype, shape in (("lambda", np.float64, (h, w)), ("lambda32", np.float32, (h, w)),
+                                  ("norm", np.float64, (h, w)), ("rgba", np.uint8, (h, w, 4))):
+            if key in want:
+                out[key] = np.empty(shape, dtype=dtype)
+                ptrs[key] = out[key].ctypes.data
+            else:
+                ptrs[key] = None
+        stats = MultiStats()
+        _check(self.lib.lyap_multi_render(self.m, ctypes.byref(params), flags, ptrs["lambda"], ptrs["lambda32"], ptrs["norm"],
+                                          ptrs["rgba"], timeout_seconds, ctypes.byref(stats)))
+        out["stats"] = stats
+        return out
+
+    def gathered(self):
+        """Device pointers (first device) of the gathered RGBA8 and fp32 lambda frames."""
+        a, b = ctypes.c_void_p(), ctypes.c_void_p()
+        _check(self.lib.lyap_multi_gathered(self.m, ctypes.byref(a), ctypes.byref(b)))
+        return a.value, b.value
+
+    def render_frames(self, frames, norm_ptrs, rgba_ptrs):
+        """lyap_multi_render_frames with caller-owned host pointers (lists of ints or None); returns the stats list."""
+        n = len(frames)
+        arr = (LyapParams * n)()
+        for i, f in enumerate(frames):
+            ctypes.memmove(ctypes.byref(arr[i]), ctypes.byref(f), ctypes.sizeof(LyapParams))
+        pn = (_P * n)(*norm_ptrs) if norm_ptrs is not None else None
+        pr = (_P * n)(*rgba_ptrs) if rgba_ptrs is not None else None
+        stats = (RenderStats * n)()
+        _check(self.lib.lyap_multi_render_frames(self.m, arr, n, pn, pr, stats))
+        return list(stats)
 
 
 class DeviceBuffer:

@@ -7,14 +7,13 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
-#include <chrono>
-#include <condition_variable>
 #include <mutex>
 #include <new>
 #include <numeric>
-#include <thread>
 #include <string>
 #include <vector>
+
+#include <nvtx3/nvToolsExt.h>   // header-only: ranges cost nothing unless a profiler attaches
 
 #include "../../include/lyap_b200.h"
 #include "lyap_engine.h"
@@ -42,6 +41,12 @@ int fail_cuda(cudaError_t e, const char* what) {
 struct Buffer {
     void* p = nullptr;
     size_t cap = 0;
+};
+
+// NVTX range around the enqueueing of one stage (shows as a named span in a profiler's timeline)
+struct Range {
+    explicit Range(const char* name) { nvtxRangePushA(name); }
+    ~Range() { nvtxRangePop(); }
 };
 
 }  // namespace
@@ -94,6 +99,10 @@ int build_args(const lyap_params* p, lyap::LambdaArgs* a, Geometry* g) {
     if (p->width < 1 || p->height < 1) return fail(LYAP_ERR_INVALID, "width and height must be >= 1");
     if (p->iterations < 0 || p->warmup < 0) return fail(LYAP_ERR_INVALID, "iterations and warmup must be >= 0");
     if (p->mode < LYAP_MODE_EXACT || p->mode > LYAP_MODE_FAST_FP32) return fail(LYAP_ERR_INVALID, "unknown mode");
+    // the fast kernels keep each pixel's exponent sum in 32 bits: a derivative's exponent is at most 2 and, short of an
+    // exact zero (handled apart), no less than about -60, so 2^24 steps stay far inside the range
+    if (p->mode != LYAP_MODE_EXACT && (long long)p->iterations + p->warmup > (1LL << 24))
+        return fail(LYAP_ERR_TOO_LARGE, "the fast modes take at most 2^24 steps per pixel (warmup + iterations)");
     if (!p->sequence) return fail(LYAP_ERR_SEQUENCE, "sequence is null");
     const long long seq_len = p->sequence_len < 0 ? (long long)std::strlen(p->sequence) : p->sequence_len;
     if (seq_len < 1) return fail(LYAP_ERR_SEQUENCE, "sequence is empty");
@@ -153,6 +162,7 @@ int build_args(const lyap_params* p, lyap::LambdaArgs* a, Geometry* g) {
 }
 
 int launch_lambda(lyap_ctx* c, int mode, const lyap::LambdaArgs& a, double* d64, float* d32, unsigned long long* steps) {
+    Range range("lyap: lambda");
     cudaError_t e;
     if (mode == LYAP_MODE_EXACT) e = lyap::launch_lambda_exact(a, d64, d32, steps, c->sm_count, c->stream);
     else if (mode == LYAP_MODE_FAST_FP64) e = lyap::launch_lambda_fast64(a, d64, d32, steps, c->sm_count, c->stream);
@@ -171,6 +181,14 @@ int check_ctx(lyap_ctx* c) {
 
 namespace lyap {
 int set_error(int status, const char* message) { return fail(status, message); }
+
+int validate_whole_frame(const lyap_params* p) {
+    LambdaArgs a;
+    Geometry g;
+    if (int r = build_args(p, &a, &g)) return r;
+    if (g.rows != p->height) return fail(LYAP_ERR_INVALID, "whole frames only here (row_begin = row_end = 0)");
+    return LYAP_OK;
+}
 }  // namespace lyap
 
 extern "C" {
@@ -180,6 +198,8 @@ int lyap_abi_version(void) { return LYAP_ABI_VERSION; }
 int lyap_self_test(void) { return 42; }
 
 const char* lyap_jit_note(void) { return lyap::jit_last_note(); }
+
+const char* lyap_last_kernel(void) { return lyap::last_lambda_kernel(); }
 
 int lyap_selector_code(const lyap_params* p, int region, int64_t step, int* code) {
     if (!code || region < 0 || region > 1) return fail(LYAP_ERR_INVALID, "lyap_selector_code: bad region or null output");
@@ -368,7 +388,8 @@ int lyap_lambda_device(lyap_ctx* c, const lyap_params* p, double* d_lambda, floa
 int lyap_minmax_device(lyap_ctx* c, const double* d_values, uint64_t n, double* d_minmax) {
     if (int r = check_ctx(c)) return r;
     if (!d_minmax || (!d_values && n)) return fail(LYAP_ERR_INVALID, "null pointer");
-    cudaError_t e = lyap::launch_minmax(d_values, n, d_minmax, ctx_scratch(c), c->stream);
+    Range range("lyap: min/max");
+    cudaError_t e = lyap::launch_minmax(d_values, n, d_minmax, ctx_scratch(c), c->sm_count, c->stream);
     if (e != cudaSuccess) return fail_cuda(e, "minmax launch");
     return LYAP_OK;
 }
@@ -377,6 +398,7 @@ int lyap_normalize_device(lyap_ctx* c, const double* d_values, uint64_t n, const
     if (int r = check_ctx(c)) return r;
     if (n == 0) return LYAP_OK;
     if (!d_values || !d_minmax || !d_out) return fail(LYAP_ERR_INVALID, "null pointer");
+    Range range("lyap: normalise");
     cudaError_t e = lyap::launch_normalize(d_values, n, d_minmax, d_out, c->sm_count, c->stream);
     if (e != cudaSuccess) return fail_cuda(e, "normalize launch");
     return LYAP_OK;
@@ -389,8 +411,9 @@ int lyap_colorize_device(lyap_ctx* c, const double* d_norm, int32_t width, int64
     if (rows == 0) return LYAP_OK;
     if (!d_norm || !d_rgba) return fail(LYAP_ERR_INVALID, "null pointer");
     if (palette < 0 || palette > LYAP_PALETTE_RAINBOW) palette = LYAP_PALETTE_COSMIC;
+    Range range("lyap: colour");
     cudaError_t e = lyap::launch_colorize(d_norm, width, rows, rows_above ? 1 : 0, rows_below ? 1 : 0, palette, d_rgba,
-                                          c->stream);
+                                          c->sm_count, c->stream);
     if (e != cudaSuccess) return fail_cuda(e, "colorize launch");
     return LYAP_OK;
 }
@@ -399,7 +422,7 @@ int lyap_glow_device(lyap_ctx* c, uint8_t* d_rgba, int32_t width, int32_t height
     if (int r = check_ctx(c)) return r;
     if (width < 1 || height < 1) return fail(LYAP_ERR_INVALID, "bad dimensions");
     if (!d_rgba || !d_scratch) return fail(LYAP_ERR_INVALID, "null pointer");
-    cudaError_t e = lyap::launch_glow(d_rgba, width, height, static_cast<double*>(d_scratch), c->stream);
+    cudaError_t e = lyap::launch_glow(d_rgba, width, height, static_cast<double*>(d_scratch), c->sm_count, c->stream);
     if (e != cudaSuccess) return fail_cuda(e, "glow launch");
     return LYAP_OK;
 }
@@ -469,9 +492,12 @@ int lyap_render(lyap_ctx* c, const lyap_params* p, double* out_lambda, float* ou
     }
     CU(cudaEventRecord(c->ev[1], st));
     if (want_colour) {
-        cudaError_t e = lyap::launch_minmax(d_lambda, n, ctx_minmax(c), ctx_scratch(c), st);
+        nvtxRangePushA("lyap: min/max");
+        cudaError_t e = lyap::launch_minmax(d_lambda, n, ctx_minmax(c), ctx_scratch(c), c->sm_count, st);
+        nvtxRangePop();
         if (e != cudaSuccess) return fail_cuda(e, "minmax launch");
         CU(cudaEventRecord(c->ev[2], st));
+        Range range("lyap: normalise");
         e = lyap::launch_normalize(d_lambda, n, ctx_minmax(c), d_norm, c->sm_count, st);
         if (e != cudaSuccess) return fail_cuda(e, "normalize launch");
         launches += 2;
@@ -482,11 +508,13 @@ int lyap_render(lyap_ctx* c, const lyap_params* p, double* out_lambda, float* ou
     if (out_rgba) {
         int pal = p->palette;
         if (pal < 0 || pal > LYAP_PALETTE_RAINBOW) pal = LYAP_PALETTE_COSMIC;
-        cudaError_t e = lyap::launch_colorize(d_norm, p->width, p->height, 0, 0, pal, d_rgba, st);
+        Range range("lyap: colour");
+        cudaError_t e = lyap::launch_colorize(d_norm, p->width, p->height, 0, 0, pal, d_rgba, c->sm_count, st);
         if (e != cudaSuccess) return fail_cuda(e, "colorize launch");
         ++launches;
     }
     CU(cudaEventRecord(c->ev[4], st));
+    Range copies("lyap: copies to host");
     if (out_lambda) CU(cudaMemcpyAsync(out_lambda, d_lambda, n * sizeof(double), cudaMemcpyDeviceToHost, st));
     if (out_lambda32) CU(cudaMemcpyAsync(out_lambda32, d_l32, n * sizeof(float), cudaMemcpyDeviceToHost, st));
     if (out_norm) CU(cudaMemcpyAsync(out_norm, d_norm, n * sizeof(double), cudaMemcpyDeviceToHost, st));
@@ -529,7 +557,7 @@ int lyap_normalize_data(lyap_ctx* c, const double* values, uint64_t n, double* o
     if (int r = ensure(c, c->norm, n * sizeof(double))) return r;
     cudaStream_t st = c->stream;
     CU(cudaMemcpyAsync(c->lambda.p, values, n * sizeof(double), cudaMemcpyHostToDevice, st));
-    cudaError_t e = lyap::launch_minmax(static_cast<double*>(c->lambda.p), n, ctx_minmax(c), ctx_scratch(c), st);
+    cudaError_t e = lyap::launch_minmax(static_cast<double*>(c->lambda.p), n, ctx_minmax(c), ctx_scratch(c), c->sm_count, st);
     if (e != cudaSuccess) return fail_cuda(e, "minmax launch");
     e = lyap::launch_normalize(static_cast<double*>(c->lambda.p), n, ctx_minmax(c), static_cast<double*>(c->norm.p),
                                c->sm_count, st);
@@ -550,7 +578,7 @@ int lyap_colorize(lyap_ctx* c, const double* norm, int32_t width, int32_t height
     cudaStream_t st = c->stream;
     CU(cudaMemcpyAsync(c->norm.p, norm, n * sizeof(double), cudaMemcpyHostToDevice, st));
     cudaError_t e = lyap::launch_colorize(static_cast<double*>(c->norm.p), width, height, 0, 0, palette,
-                                          static_cast<uint8_t*>(c->rgba.p), st);
+                                          static_cast<uint8_t*>(c->rgba.p), c->sm_count, st);
     if (e != cudaSuccess) return fail_cuda(e, "colorize launch");
     CU(cudaMemcpyAsync(out_rgba, c->rgba.p, n * 4, cudaMemcpyDeviceToHost, st));
     CU(cudaStreamSynchronize(st));
@@ -558,345 +586,6 @@ int lyap_colorize(lyap_ctx* c, const double* norm, int32_t width, int32_t height
 }
 
 }  // extern "C"
-
-// ---- one frame over several devices ----
-
-namespace {
-
-struct MultiShared {
-    std::mutex mu;
-    std::condition_variable cv;
-    int arrived = 0, expected = 0;
-    bool failed = false;
-    double lo = 0, hi = 0;
-    bool have = false;
-    unsigned long long steps = 0;
-    int status = LYAP_OK;
-    std::string error;
-};
-
-void multi_fail(MultiShared& sh, int status, const char* msg) {
-    std::lock_guard<std::mutex> lk(sh.mu);
-    if (sh.status == LYAP_OK) {
-        sh.status = status;
-        sh.error = msg;
-    }
-    sh.failed = true;
-    sh.cv.notify_all();
-}
-
-// One band on one device.  Returns after its part of the host buffers is written, or after a failure anywhere.
-void multi_worker(MultiShared& sh, const lyap_params& base, int device, long long b0, long long b1, double* out_lambda,
-                  double* out_norm, uint8_t* out_rgba, double timeout_s) {
-    lyap_ctx* c = nullptr;
-    if (lyap_create(&c, device) != LYAP_OK) return multi_fail(sh, LYAP_ERR_CUDA, lyap_last_error());
-    const long long H = base.height, W = base.width;
-    const int above = b0 > 0 ? 1 : 0, below = b1 < H ? 1 : 0;
-    const long long rows_all = (b1 - b0) + above + below, rows_own = b1 - b0;
-    // one device allocation for the band: lambda | normalised | RGBA | min/max + step counter (allocations are
-    // serialised across the workers of a process, so they are kept few)
-    void *block = nullptr, *d_lam = nullptr, *d_norm = nullptr, *d_rgba = nullptr, *d_small = nullptr;
-    auto cleanup = [&]() {
-        if (block) lyap_device_free(c, block);
-        lyap_destroy(c);
-    };
-    auto bail = [&](int st) {
-        multi_fail(sh, st, lyap_last_error());
-        cleanup();
-    };
-    const bool colour = out_norm || out_rgba;
-    const size_t lam_bytes = ((size_t)rows_all * W * 8 + 255) / 256 * 256;
-    const size_t norm_bytes = colour ? lam_bytes : 0;
-    const size_t rgba_bytes = out_rgba ? ((size_t)rows_own * W * 4 + 255) / 256 * 256 : 0;
-    int st = lyap_device_alloc(c, &block, lam_bytes + norm_bytes + rgba_bytes + 256);
-    if (st != LYAP_OK) return bail(st);
-    d_lam = block;
-    d_norm = colour ? static_cast<char*>(block) + lam_bytes : nullptr;
-    d_rgba = out_rgba ? static_cast<char*>(block) + lam_bytes + norm_bytes : nullptr;
-    d_small = static_cast<char*>(block) + lam_bytes + norm_bytes + rgba_bytes;
-    double* d_mm = static_cast<double*>(d_small);
-    uint64_t* d_steps = reinterpret_cast<uint64_t*>(d_mm + 2);
-    uint64_t zero = 0;
-    double* own = static_cast<double*>(d_lam) + (size_t)above * W;
-    st = lyap_copy_to_device(c, d_steps, &zero, 8);
-    {   // the band's own rows (counted), then the halo rows (same kernel, not counted)
-        lyap_params p = base;
-        p.row_begin = b0;
-        p.row_end = b1;
-        if (st == LYAP_OK) st = lyap_lambda_device(c, &p, own, nullptr, d_steps);
-        if (st == LYAP_OK && above) {
-            p.row_begin = b0 - 1;
-            p.row_end = b0;
-            st = lyap_lambda_device(c, &p, static_cast<double*>(d_lam), nullptr, nullptr);
-        }
-        if (st == LYAP_OK && below) {
-            p.row_begin = b1;
-            p.row_end = b1 + 1;
-            st = lyap_lambda_device(c, &p, own + (size_t)rows_own * W, nullptr, nullptr);
-        }
-    }
-    if (st == LYAP_OK) st = lyap_minmax_device(c, own, (uint64_t)rows_own * W, d_mm);
-    double mm[2];
-    uint64_t steps = 0;
-    if (st == LYAP_OK) st = lyap_copy_to_host(c, mm, d_mm, 16);
-    if (st == LYAP_OK) st = lyap_copy_to_host(c, &steps, d_steps, 8);
-    if (st != LYAP_OK) return bail(st);
-    {   // the one exchange: min of mins, max of maxes, with a deadline
-        std::unique_lock<std::mutex> lk(sh.mu);
-        sh.lo = sh.have ? std::fmin(sh.lo, mm[0]) : mm[0];
-        sh.hi = sh.have ? std::fmax(sh.hi, mm[1]) : mm[1];
-        sh.have = true;
-        sh.steps += steps;
-        ++sh.arrived;
-        sh.cv.notify_all();
-        const bool ok = sh.cv.wait_for(lk, std::chrono::duration<double>(timeout_s),
-                                       [&] { return sh.arrived == sh.expected || sh.failed; });
-        if (!ok && sh.status == LYAP_OK) {
-            sh.status = LYAP_ERR_TIMEOUT;
-            sh.error = "lyap_render_multi: a band did not reach the min/max exchange before the deadline";
-            sh.failed = true;
-            sh.cv.notify_all();
-        }
-        if (sh.failed) {
-            lk.unlock();
-            cleanup();
-            return;
-        }
-        mm[0] = sh.lo;
-        mm[1] = sh.hi;
-    }
-    if (out_lambda) st = lyap_copy_to_host(c, out_lambda + (size_t)b0 * W, own, (size_t)rows_own * W * 8);
-    if (st == LYAP_OK && colour) {
-        st = lyap_copy_to_device(c, d_mm, mm, 16);
-        if (st == LYAP_OK) st = lyap_normalize_device(c, static_cast<double*>(d_lam), (uint64_t)rows_all * W, d_mm, static_cast<double*>(d_norm));
-        double* norm_own = static_cast<double*>(d_norm) + (size_t)above * W;
-        if (st == LYAP_OK && out_rgba)
-            st = lyap_colorize_device(c, norm_own, base.width, rows_own, above, below, base.palette, static_cast<uint8_t*>(d_rgba));
-        if (st == LYAP_OK && out_norm) st = lyap_copy_to_host(c, out_norm + (size_t)b0 * W, norm_own, (size_t)rows_own * W * 8);
-        if (st == LYAP_OK && out_rgba) st = lyap_copy_to_host(c, out_rgba + (size_t)b0 * W * 4, d_rgba, (size_t)rows_own * W * 4);
-    }
-    if (st != LYAP_OK) return bail(st);
-    cleanup();
-}
-
-}  // namespace
-
-extern "C" int lyap_render_multi(const lyap_params* p, int32_t n_devices, const int32_t* devices, double* out_lambda,
-                                 double* out_norm, uint8_t* out_rgba, double timeout_seconds, lyap_render_stats* stats) {
-    lyap::LambdaArgs args;
-    Geometry g;
-    if (int r = build_args(p, &args, &g)) return r;
-    if (g.rows != p->height) return fail(LYAP_ERR_INVALID, "lyap_render_multi renders whole frames (row_begin = row_end = 0)");
-    if (n_devices < 1 || !devices) return fail(LYAP_ERR_INVALID, "need at least one device");
-    if (n_devices > p->height) return fail(LYAP_ERR_INVALID, "more bands than rows");
-    if (timeout_seconds <= 0) timeout_seconds = 60.0;
-    const auto t0 = std::chrono::steady_clock::now();
-    MultiShared sh;
-    sh.expected = n_devices;
-    std::vector<std::thread> workers;
-    const long long H = p->height, base = H / n_devices, extra = H % n_devices;
-    for (int r = 0; r < n_devices; ++r) {
-        const long long b0 = r * base + (r < extra ? r : extra);
-        const long long b1 = b0 + base + (r < extra ? 1 : 0);
-        if (devices[r] < 0) continue;   // a band whose worker never arrives
-        workers.emplace_back(multi_worker, std::ref(sh), std::cref(*p), (int)devices[r], b0, b1, out_lambda, out_norm,
-                             out_rgba, timeout_seconds);
-    }
-    for (auto& w : workers) w.join();
-    if (workers.empty()) return fail(LYAP_ERR_TIMEOUT, "lyap_render_multi: no band arrived");
-    if (sh.status != LYAP_OK) return fail(sh.status, sh.error);
-    if (stats) {
-        std::memset(stats, 0, sizeof(*stats));
-        stats->executed_steps = sh.steps;
-        stats->nominal_steps = (uint64_t)g.n_pixels * (uint64_t)((long long)p->warmup + p->iterations);
-        stats->lambda_min = sh.lo;
-        stats->lambda_max = sh.hi;
-        stats->ms_total_device = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
-        stats->kernel_launches = 6 * n_devices - 2;   // per band: lambda for own rows + up to two halo rows, min/max, normalise, colour
-    }
-    return LYAP_OK;
-}
-
-// ---- a batch of independent frames (a zoom sequence) over several devices ----
-
-namespace {
-
-struct FramesShared {
-    std::mutex mu;
-    bool failed = false;
-    int status = LYAP_OK;
-    std::string error;
-};
-
-void frames_fail(FramesShared& sh, int status, const char* msg) {
-    std::lock_guard<std::mutex> lk(sh.mu);
-    if (sh.status == LYAP_OK) {
-        sh.status = status;
-        sh.error = msg;
-    }
-    sh.failed = true;
-}
-
-struct FrameSmall {
-    double mm[2];
-    unsigned long long steps;
-};
-
-// One set of device buffers; a worker alternates between two, so that one frame's copies to the host run
-// while the next frame is computed.
-struct FrameSlot {
-    void* block = nullptr;           // one device allocation: lambda | normalised | RGBA | min/max + step counter
-    void *lam = nullptr, *norm = nullptr, *rgba = nullptr, *small = nullptr;
-    FrameSmall* h_small = nullptr;   // pinned, owned by the caller of the workers
-    cudaEvent_t begun = nullptr, lambda_done = nullptr, computed = nullptr, copied = nullptr;
-    int frame = -1;
-};
-
-// Frames first, first + stride, ... on one device: kernels in order on the context's stream, copies on a second
-// stream behind an event, two buffer sets.
-void frames_worker(FramesShared& sh, int device, int first, int stride, const lyap_params* frames, int n_frames,
-                   double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats, FrameSmall* pinned) {
-    lyap_ctx* c = nullptr;
-    if (lyap_create(&c, device) != LYAP_OK) return frames_fail(sh, LYAP_ERR_CUDA, lyap_last_error());
-    cudaStream_t copy = nullptr;
-    FrameSlot slots[2];
-    size_t max_px = 0;
-    bool any_rgba = false;
-    for (int k = first; k < n_frames; k += stride) {
-        max_px = std::max(max_px, (size_t)frames[k].width * (size_t)frames[k].height);
-        any_rgba = any_rgba || (out_rgba && out_rgba[k]);
-    }
-    auto cleanup = [&]() {
-        cudaStreamSynchronize(c->stream);
-        if (copy) cudaStreamSynchronize(copy);
-        for (FrameSlot& s : slots) {
-            if (s.block) cudaFree(s.block);
-            for (cudaEvent_t e : {s.begun, s.lambda_done, s.computed, s.copied})
-                if (e) cudaEventDestroy(e);
-        }
-        if (copy) cudaStreamDestroy(copy);
-        lyap_destroy(c);
-    };
-    auto bail_cuda = [&](cudaError_t e, const char* what) {
-        fail_cuda(e, what);
-        frames_fail(sh, LYAP_ERR_CUDA, lyap_last_error());
-        cleanup();
-    };
-#define FR(call)                                                   \
-    do {                                                           \
-        cudaError_t fr_e = (call);                                 \
-        if (fr_e != cudaSuccess) return bail_cuda(fr_e, #call);    \
-    } while (0)
-    FR(cudaStreamCreateWithFlags(&copy, cudaStreamNonBlocking));
-    // allocations are few on purpose: with several devices in one process every cudaMalloc / cudaFree and, far more,
-    // every pinned allocation is serialised across the workers
-    const size_t px8 = (max_px * 8 + 255) / 256 * 256, px4 = any_rgba ? (max_px * 4 + 255) / 256 * 256 : 0;
-    for (int i = 0; i < 2; ++i) {
-        FrameSlot& s = slots[i];
-        FR(cudaMalloc(&s.block, 2 * px8 + px4 + 256));
-        char* base = static_cast<char*>(s.block);
-        s.lam = base;
-        s.norm = base + px8;
-        s.rgba = any_rgba ? base + 2 * px8 : nullptr;
-        s.small = base + 2 * px8 + px4;
-        s.h_small = pinned + i;
-        for (cudaEvent_t* e : {&s.begun, &s.lambda_done, &s.computed, &s.copied}) FR(cudaEventCreate(e));
-    }
-    // the slot's frame has reached the host: fill in its statistics
-    auto finish = [&](FrameSlot& s) -> cudaError_t {
-        if (s.frame < 0) return cudaSuccess;
-        cudaError_t e = cudaEventSynchronize(s.copied);
-        if (e != cudaSuccess) return e;
-        if (stats) {
-            const lyap_params& p = frames[s.frame];
-            lyap_render_stats& r = stats[s.frame];
-            std::memset(&r, 0, sizeof(r));
-            r.executed_steps = s.h_small->steps;
-            r.nominal_steps = (uint64_t)p.width * (uint64_t)p.height * (uint64_t)((long long)p.warmup + p.iterations);
-            r.lambda_min = s.h_small->mm[0];
-            r.lambda_max = s.h_small->mm[1];
-            cudaEventElapsedTime(&r.ms_lambda, s.begun, s.lambda_done);
-            cudaEventElapsedTime(&r.ms_total_device, s.begun, s.computed);
-            cudaEventElapsedTime(&r.ms_copies, s.computed, s.copied);
-            r.kernel_launches = (out_rgba && out_rgba[s.frame]) ? 4 : 3;
-        }
-        s.frame = -1;
-        return cudaSuccess;
-    };
-    int local = 0;
-    for (int k = first; k < n_frames; k += stride, ++local) {
-        {
-            std::lock_guard<std::mutex> lk(sh.mu);
-            if (sh.failed) break;
-        }
-        FrameSlot& s = slots[local & 1];
-        FR(finish(s));   // its buffers are free again
-        const lyap_params& p = frames[k];
-        const size_t n = (size_t)p.width * (size_t)p.height;
-        double* d_mm = static_cast<double*>(s.small);
-        uint64_t* d_steps = reinterpret_cast<uint64_t*>(d_mm + 2);
-        cudaStream_t st = c->stream;
-        FR(cudaMemsetAsync(d_steps, 0, 8, st));
-        FR(cudaEventRecord(s.begun, st));
-        int rc = lyap_lambda_device(c, &p, static_cast<double*>(s.lam), nullptr, d_steps);
-        if (rc == LYAP_OK) {
-            FR(cudaEventRecord(s.lambda_done, st));
-            rc = lyap_minmax_device(c, static_cast<double*>(s.lam), n, d_mm);
-        }
-        if (rc == LYAP_OK) rc = lyap_normalize_device(c, static_cast<double*>(s.lam), n, d_mm, static_cast<double*>(s.norm));
-        uint8_t* h_rgba = out_rgba ? out_rgba[k] : nullptr;
-        double* h_norm = out_norm ? out_norm[k] : nullptr;
-        if (rc == LYAP_OK && h_rgba)
-            rc = lyap_colorize_device(c, static_cast<double*>(s.norm), p.width, p.height, 0, 0, p.palette, static_cast<uint8_t*>(s.rgba));
-        if (rc != LYAP_OK) {
-            frames_fail(sh, rc, lyap_last_error());
-            cleanup();
-            return;
-        }
-        FR(cudaEventRecord(s.computed, st));
-        FR(cudaStreamWaitEvent(copy, s.computed, 0));
-        if (h_norm) FR(cudaMemcpyAsync(h_norm, s.norm, n * 8, cudaMemcpyDeviceToHost, copy));
-        if (h_rgba) FR(cudaMemcpyAsync(h_rgba, s.rgba, n * 4, cudaMemcpyDeviceToHost, copy));
-        FR(cudaMemcpyAsync(s.h_small, s.small, sizeof(FrameSmall), cudaMemcpyDeviceToHost, copy));
-        FR(cudaEventRecord(s.copied, copy));
-        s.frame = k;
-    }
-    for (FrameSlot& s : slots) FR(finish(s));
-#undef FR
-    cleanup();
-}
-
-}  // namespace
-
-extern "C" int lyap_render_frames(const lyap_params* frames, int32_t n_frames, int32_t n_devices, const int32_t* devices,
-                                  double* const* out_norm, uint8_t* const* out_rgba, lyap_render_stats* stats) {
-    if (n_frames < 0 || (n_frames > 0 && !frames)) return fail(LYAP_ERR_INVALID, "lyap_render_frames: bad frame list");
-    if (n_devices < 1 || !devices) return fail(LYAP_ERR_INVALID, "need at least one device");
-    for (int k = 0; k < n_frames; ++k) {
-        lyap::LambdaArgs a;
-        Geometry g;
-        if (int r = build_args(&frames[k], &a, &g)) return r;
-        if (g.rows != frames[k].height)
-            return fail(LYAP_ERR_INVALID, "lyap_render_frames renders whole frames (row_begin = row_end = 0)");
-    }
-    if (n_frames == 0) return LYAP_OK;
-    // one pinned block for every worker's two small read-back records
-    int n_dev_present = 0;
-    CU(cudaGetDeviceCount(&n_dev_present));
-    if (devices[0] < 0 || devices[0] >= n_dev_present) return fail(LYAP_ERR_INVALID, "no such device");
-    CU(cudaSetDevice(devices[0]));
-    FrameSmall* pinned = nullptr;
-    CU(cudaMallocHost(reinterpret_cast<void**>(&pinned), (size_t)n_devices * 2 * sizeof(FrameSmall)));
-    FramesShared sh;
-    std::vector<std::thread> workers;
-    for (int r = 0; r < n_devices && r < n_frames; ++r)
-        workers.emplace_back(frames_worker, std::ref(sh), (int)devices[r], r, (int)n_devices, frames, (int)n_frames, out_norm,
-                             out_rgba, stats, pinned + 2 * r);
-    for (auto& w : workers) w.join();
-    cudaFreeHost(pinned);
-    if (sh.status != LYAP_OK) return fail(sh.status, sh.error);
-    return LYAP_OK;
-}
 
 extern "C" {
 
@@ -909,7 +598,7 @@ int lyap_glow(lyap_ctx* c, const uint8_t* rgba_in, int32_t width, int32_t height
     if (int r = ensure(c, c->norm, n * 24)) return r;   // the blur's scratch shares the normalised-frame buffer
     cudaStream_t st = c->stream;
     CU(cudaMemcpyAsync(c->rgba.p, rgba_in, n * 4, cudaMemcpyHostToDevice, st));
-    cudaError_t e = lyap::launch_glow(static_cast<uint8_t*>(c->rgba.p), width, height, static_cast<double*>(c->norm.p), st);
+    cudaError_t e = lyap::launch_glow(static_cast<uint8_t*>(c->rgba.p), width, height, static_cast<double*>(c->norm.p), c->sm_count, st);
     if (e != cudaSuccess) return fail_cuda(e, "glow launch");
     CU(cudaMemcpyAsync(rgba_out, c->rgba.p, n * 4, cudaMemcpyDeviceToHost, st));
     CU(cudaStreamSynchronize(st));

@@ -34,13 +34,14 @@ struct Options {
     double c = 0.0;
     int gpus = 1, frame = 0, frames = 0, repeat = 1;
     bool glow = false;
+    bool gather = false;
 };
 
 [[noreturn]] void usage(const char* why) {
     std::cerr << "lyap_cli: " << why << "\n"
               << "usage: lyap_cli [--config 1..5 [--frame K] [--frames N [--repeat R]]] [--width W --height H --min-x .. --max-x .. --min-y .. --max-y ..]\n"
               << "                [--sequence S] [--iterations N] [--warmup N] [--c V] [--palette NAME]\n"
-              << "                [--mode exact|fast64|fast32] [--gpus N] [--glow] [--out file.ppm|.rgba|.f64]\n";
+              << "                [--mode exact|fast64|fast32] [--gpus N [--gather] [--repeat R]] [--glow] [--out file.ppm|.rgba|.f64]\n";
     std::exit(2);
 }
 
@@ -60,6 +61,15 @@ void apply_config(Options& o, int n) {
         } break;
         default: usage("--config takes 1..5");
     }
+}
+
+std::string json_escape(std::string_view s) {
+    std::string out;
+    for (char ch : s) {
+        if (ch == '"' || ch == '\\') out += '\\';
+        out += ch;
+    }
+    return out;
 }
 
 double to_double(std::string_view s) {
@@ -181,6 +191,7 @@ int main(int argc, char** argv) {
         else if (a == "--gpus") o.gpus = to_int(next());
         else if (a == "--out") o.out = std::string(next());
         else if (a == "--glow") o.glow = true;
+        else if (a == "--gather") o.gather = true;
         else usage("unknown option");
     }
 
@@ -203,6 +214,8 @@ int main(int argc, char** argv) {
     std::vector<double> norm(want_f64 ? n : 0);
     std::vector<uint8_t> rgba(n * 4);
     lyap_render_stats st{};
+    lyap_multi_stats ms{};
+    std::string multi_note;
     const auto t0 = std::chrono::steady_clock::now();
     int status;
     if (o.gpus <= 1) {
@@ -214,9 +227,21 @@ int main(int argc, char** argv) {
             lyap_destroy(ctx);
         }
     } else {
+        // one frame as row bands over the devices; --gather collects the RGBA8 bands in device 0's memory first (NCCL
+        // send/recv) and copies the frame to the host from there; --repeat renders it again on the same object
         std::vector<int32_t> devs(o.gpus);
         for (int i = 0; i < o.gpus; ++i) devs[i] = i;
-        status = lyap_render_multi(&p, o.gpus, devs.data(), nullptr, want_f64 ? norm.data() : nullptr, rgba.data(), 0.0, &st);
+        lyap_multi* m = nullptr;
+        if ((status = lyap_multi_create(&m, o.gpus, devs.data(), o.gather ? 1 : 0)) == LYAP_OK) {
+            for (int pass = 0; pass < std::max(1, o.repeat) && status == LYAP_OK; ++pass)
+                status = lyap_multi_render(m, &p, o.gather ? LYAP_MULTI_GATHER_RGBA : 0, nullptr, nullptr,
+                                           want_f64 ? norm.data() : nullptr, rgba.data(), 0.0, &ms);
+            multi_note = lyap_multi_note(m);
+            lyap_multi_destroy(m);
+        }
+        st.executed_steps = ms.executed_steps; st.nominal_steps = ms.nominal_steps;
+        st.lambda_min = ms.lambda_min; st.lambda_max = ms.lambda_max;
+        st.ms_lambda = ms.ms_lambda_max; st.ms_total_device = ms.ms_device_max;
     }
     if (status == LYAP_OK && o.glow) {   // the page's last step (web/fractal_renderer.js:203)
         lyap_ctx* ctx = nullptr;
@@ -242,8 +267,10 @@ int main(int argc, char** argv) {
     std::cout << std::format(
         "{{\"width\": {}, \"height\": {}, \"sequence\": \"{}\", \"mode\": \"{}\", \"gpus\": {}, \"executed_steps\": {}, "
         "\"nominal_steps\": {}, \"lambda_min\": {}, \"lambda_max\": {}, \"ms_lambda\": {:.3f}, \"ms_device\": {:.3f}, "
-        "\"ms_wall\": {:.3f}, \"steps_per_s_wall\": {:.4e}}}\n",
+        "\"ms_wall\": {:.3f}, \"steps_per_s_wall\": {:.4e}, \"ms_render_last_pass\": {:.3f}, \"gather_ms\": {:.3f}, "
+        "\"gather_bytes\": {}, \"gather_gbs\": {:.1f}, \"used_nccl\": {}, \"multi_note\": \"{}\", \"kernel\": \"{}\"}}\n",
         o.width, o.height, o.sequence, o.mode, o.gpus, st.executed_steps, st.nominal_steps, st.lambda_min, st.lambda_max,
-        st.ms_lambda, st.ms_total_device, wall_ms, st.executed_steps / (wall_ms * 1e-3));
+        st.ms_lambda, st.ms_total_device, wall_ms, st.executed_steps / (wall_ms * 1e-3), ms.ms_wall, ms.ms_gather, ms.gather_bytes,
+        ms.ms_gather > 0 ? ms.gather_bytes / (ms.ms_gather * 1e-3) / 1e9 : 0.0, ms.used_nccl, multi_note, json_escape(lyap_last_kernel()));
     return 0;
 }

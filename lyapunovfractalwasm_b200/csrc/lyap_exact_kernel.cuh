@@ -9,7 +9,7 @@
 
 namespace lyap {
 
-__device__ const lyap_logtab_entry g_lyap_logtab[LYAP_LOG_BINS] = {LYAP_LOG_TABLE_INIT};
+static __device__ const lyap_logtab_entry g_lyap_logtab[LYAP_LOG_BINS] = {LYAP_LOG_TABLE_INIT};
 
 // ---------------------------------------------------------------------------------------------
 // Exact lambda kernel.
@@ -42,6 +42,10 @@ constexpr size_t kTabSmemBytes = (size_t)LYAP_LOG_BINS * kTabCopies * sizeof(lya
 constexpr int kExpEntries = 4096;
 constexpr size_t kExpSmemBytes = (size_t)kExpEntries * sizeof(double2);                              // 64 KB
 constexpr size_t kExactSmemBytes = kTabSmemBytes + kExpSmemBytes;
+// after the tables: one tile of results (THREADS * P doubles) staged for 16-byte-per-lane stores
+__host__ __device__ constexpr size_t exact_smem_bytes(int threads, int pixels_per_thread) {
+    return kExactSmemBytes + (size_t)threads * pixels_per_thread * sizeof(double);
+}
 
 __device__ __forceinline__ bool in_unit_interval(double x) { return x > 0.0 && x < 1.0; }
 
@@ -94,8 +98,8 @@ __device__ __noinline__ bool careful_chunk(PixelState* ps, double rA, double rB,
 struct LogConsts {
     double c2, c3, c4, ln2hi, ln2lo, klo_bias;
 };
-__constant__ LogConsts c_logk = {LYAP_LOG_C2, LYAP_LOG_C3, LYAP_LOG_C4, LYAP_LN2HI, LYAP_LN2LO, LYAP_KLO_BIAS};
-__constant__ int c_minus_2p20 = -(1 << 20);   // read as a constant-bank operand so the product below stays one multiply-add
+static __constant__ LogConsts c_logk = {LYAP_LOG_C2, LYAP_LOG_C3, LYAP_LOG_C4, LYAP_LN2HI, LYAP_LN2LO, LYAP_KLO_BIAS};
+static __constant__ int c_minus_2p20 = -(1 << 20);   // read as a constant-bank operand so the product below stays one multiply-add
 
 // lyap_log_core (lyap_math.h) for a positive normal d, written against the two shared-memory tables, which start
 // at the beginning of the dynamic shared memory: `lane_off` is the byte offset of this lane's copy inside a
@@ -315,7 +319,6 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
         t.invc = __hiloint2double(__double2hiint(t.invc) + 0x3FF00000, __double2loint(t.invc));   // see log_fast
         tab_all[e] = t;
     }
-    __syncthreads();
     const unsigned lane_off = (threadIdx.x & (kTabCopies - 1)) * 16u;
     double2* exp_tab = reinterpret_cast<double2*>(smem_raw + kTabSmemBytes);
     for (int e = threadIdx.x; e < kExpEntries; e += THREADS) {
@@ -325,6 +328,7 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
         else v = make_double2(__dmul_rn((double)e, LYAP_LN2HI), __fma_rn((double)e, LYAP_LN2LO, LYAP_KLO_BIAS));
         exp_tab[e] = v;
     }
+    __syncthreads();   // both tables are read across warps from the first logarithm on (at once when warmup == 0)
 
     unsigned long long my_steps = 0;
     const long long tile_px = (long long)THREADS * P;
@@ -493,12 +497,22 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
             if (!done[p]) lam[p] = valid[p] > 0 ? __ddiv_rn(lyap[p], __dmul_rn((double)valid[p], LYAP_LN2)) : -5.0;
         }
 
-        // stores: one 16-byte (fp64) / 8-byte (fp32) store per pixel pair when aligned
+        // stores: the tile's THREADS*P consecutive values go through a staging row in shared memory so that every lane
+        // writes 16 bytes and a warp's store covers 512 consecutive bytes, whatever P is; a ragged last tile or an
+        // output pointer that is not 16-byte aligned takes plain stores
+        const long long tile0 = tile * tile_px;
+        const bool full_tile = tile0 + tile_px <= a.n_pixels;
+        double* stage = reinterpret_cast<double*>(smem_raw + kExactSmemBytes);
         if (out64) {
-            if (P % 2 == 0 && idx0 + P <= a.n_pixels && ((reinterpret_cast<uintptr_t>(out64 + idx0) & 15) == 0)) {
+            if (full_tile && ((reinterpret_cast<uintptr_t>(out64 + tile0) & 15) == 0)) {
+                __syncthreads();   // the staging row is free (previous tile's readers are done)
 #pragma unroll
-                for (int p = 0; p < P; p += 2)
-                    *reinterpret_cast<double2*>(out64 + idx0 + p) = make_double2(lam[p], lam[p + 1 < P ? p + 1 : p]);
+                for (int p = 0; p < P; ++p) stage[threadIdx.x * P + p] = lam[p];
+                __syncthreads();
+                double2* dst = reinterpret_cast<double2*>(out64 + tile0);
+                const double2* src = reinterpret_cast<const double2*>(stage);
+#pragma unroll
+                for (int i = threadIdx.x; i < THREADS * P / 2; i += THREADS) dst[i] = src[i];
             } else {
 #pragma unroll
                 for (int p = 0; p < P; ++p)
@@ -506,11 +520,16 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
             }
         }
         if (out32) {
-            if (P % 2 == 0 && idx0 + P <= a.n_pixels && ((reinterpret_cast<uintptr_t>(out32 + idx0) & 7) == 0)) {
+            if (full_tile && ((reinterpret_cast<uintptr_t>(out32 + tile0) & 15) == 0)) {
+                float* stage32 = reinterpret_cast<float*>(stage);
+                __syncthreads();
 #pragma unroll
-                for (int p = 0; p < P; p += 2)
-                    *reinterpret_cast<float2*>(out32 + idx0 + p) =
-                        make_float2((float)lam[p], (float)lam[p + 1 < P ? p + 1 : p]);
+                for (int p = 0; p < P; ++p) stage32[threadIdx.x * P + p] = (float)lam[p];
+                __syncthreads();
+                float4* dst = reinterpret_cast<float4*>(out32 + tile0);
+                const float4* src = reinterpret_cast<const float4*>(stage32);
+#pragma unroll
+                for (int i = threadIdx.x; i < THREADS * P / 4; i += THREADS) dst[i] = src[i];
             } else {
 #pragma unroll
                 for (int p = 0; p < P; ++p)

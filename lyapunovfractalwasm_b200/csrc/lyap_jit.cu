@@ -43,6 +43,7 @@ struct Nvrtc {
 
 struct Driver {
     CUresult (*module_load_data)(CUmodule*, const void*) = nullptr;
+    CUresult (*module_unload)(CUmodule) = nullptr;
     CUresult (*module_get_function)(CUfunction*, CUmodule, const char*) = nullptr;
     CUresult (*func_set_attribute)(CUfunction, CUfunction_attribute, int) = nullptr;
     CUresult (*launch_kernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
@@ -88,6 +89,7 @@ Driver& driver() {
                    st == cudaDriverEntryPointSuccess && *fn;
         };
         r.ok = get("cuModuleLoadData", reinterpret_cast<void**>(&r.module_load_data)) &&
+               get("cuModuleUnload", reinterpret_cast<void**>(&r.module_unload)) &&
                get("cuModuleGetFunction", reinterpret_cast<void**>(&r.module_get_function)) &&
                get("cuFuncSetAttribute", reinterpret_cast<void**>(&r.func_set_attribute)) &&
                get("cuLaunchKernel", reinterpret_cast<void**>(&r.launch_kernel));
@@ -171,9 +173,14 @@ bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
     CUmodule mod = nullptr;
     if (d.module_load_data(&mod, cubin.data()) != CUDA_SUCCESS) { g_note = "cuModuleLoadData failed"; return false; }
     CUfunction fn = nullptr;
-    if (d.module_get_function(&fn, mod, kind == 0 ? "k_lambda_exact_spec" : "k_lambda_fast_spec") != CUDA_SUCCESS) { g_note = "kernel symbol not found"; return false; }
+    if (d.module_get_function(&fn, mod, kind == 0 ? "k_lambda_exact_spec" : "k_lambda_fast_spec") != CUDA_SUCCESS) {
+        g_note = "kernel symbol not found";
+        d.module_unload(mod);
+        return false;
+    }
     if (smem_bytes && d.func_set_attribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)smem_bytes) != CUDA_SUCCESS) {
         g_note = "cuFuncSetAttribute failed";
+        d.module_unload(mod);
         return false;
     }
     e->fn = fn;
@@ -182,7 +189,26 @@ bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
 
 }  // namespace
 
-const char* jit_last_note() { return g_note.c_str(); }
+// The note is written by whichever thread compiled or launched last; a reader gets its own copy.
+const char* jit_last_note() {
+    thread_local std::string copy;
+    std::lock_guard<std::mutex> lk(g_mu);
+    copy = g_note;
+    return copy.c_str();
+}
+
+namespace {
+thread_local std::string t_last_kernel;
+std::vector<PrebuiltKernel>& prebuilt_list() {
+    static std::vector<PrebuiltKernel> v;
+    return v;
+}
+}  // namespace
+
+const char* last_lambda_kernel() { return t_last_kernel.c_str(); }
+void note_lambda_kernel(const char* text) { t_last_kernel = text; }
+
+void register_prebuilt(const PrebuiltKernel& k) { prebuilt_list().push_back(k); }   // static initialisers only
 
 // Finds the group-pattern period of both regions of `a`.  Returns KG (1..16) and the two pattern words, or 0.
 int sequence_group_period(const LambdaArgs& a, unsigned long long* wu_pats, unsigned long long* acc_pats) {
@@ -218,10 +244,45 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
                                cudaStream_t st, int kind, int pixels_per_thread, int threads, size_t smem_bytes, int mode,
                                bool* launched) {
     *launched = false;
-    if (mode <= 0) return cudaSuccess;
+    const int jit_mode = mode & 3;
+    if (mode == 0) return cudaSuccess;
     unsigned long long wu = 0, acc = 0;
     const int kg = sequence_group_period(a, &wu, &acc);
     if (kg == 0) return cudaSuccess;
+    const long long tile_px = (long long)threads * pixels_per_thread;
+    const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
+    const long long cap = kind == 0 ? sm_count : 4LL * sm_count;   // the exact kernel's shared tables allow one CTA per SM
+    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
+    char name[160];
+    static const char* const kinds[3] = {"k_lambda_exact", "k_lambda_fast<double>", "k_lambda_fast<float>"};
+
+    if (mode & kSpecUsePrebuilt) {   // an instance compiled with the library
+        for (const PrebuiltKernel& k : prebuilt_list()) {
+            // a region shorter than one period never runs its straight-line block (it is walked step by step from the
+            // selector words), so its patterns need not match; whether a third parameter occurs must match in any case
+            const int bs = 2 * kg;
+            const bool uses_c = ((wu | acc) & 0xAAAAAAAAAAAAAAAAull) != 0, k_uses_c = ((k.wu_pats | k.acc_pats) & 0xAAAAAAAAAAAAAAAAull) != 0;
+            if (k.kind != kind || k.pixels_per_thread != pixels_per_thread || k.threads != threads || k.kg != kg ||
+                (a.warmup >= bs && k.wu_pats != wu) || (a.iterations >= bs && k.acc_pats != acc) || uses_c != k_uses_c)
+                continue;
+            if (tiles > 0) {
+                if (smem_bytes) {
+                    const cudaError_t ae = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+                    if (ae != cudaSuccess) return ae;
+                }
+                void* params[] = {const_cast<LambdaArgs*>(&a), &out64, &out32, &steps};
+                const cudaError_t le = cudaLaunchKernel(k.fn, dim3(grid), dim3((unsigned)threads), params, smem_bytes, st);
+                if (le != cudaSuccess) return le;
+            }
+            snprintf(name, sizeof name, "%s_seq<%d px/thread, period %d steps> (built for the patterns of \"%s\")", kinds[kind],
+                     pixels_per_thread, 2 * kg, k.sequence);
+            note_lambda_kernel(name);
+            *launched = true;
+            return cudaSuccess;
+        }
+    }
+    if (jit_mode == 0) return cudaSuccess;
+
     int dev = 0;
     cudaError_t ce = cudaGetDevice(&dev);
     if (ce != cudaSuccess) return ce;
@@ -231,17 +292,18 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
         std::lock_guard<std::mutex> lk(g_mu);
         Entry& e = g_cache[key];
         e.work_seen += (double)a.n_pixels * ((double)a.warmup + a.iterations);
-        if (!e.fn && !e.failed && (mode >= 2 || e.work_seen >= 2e10)) {
+        // compiling takes about a second, so it waits until that much work with these patterns has been asked for;
+        // code another device of this process already compiled is only loaded, which is cheap
+        const CodeKey ck{pixels_per_thread, kg, wu, acc, kind, threads};
+        const auto have = g_cubins.find(ck);
+        const bool cubin_ready = have != g_cubins.end() && !have->second.empty();
+        if (!e.fn && !e.failed && (jit_mode >= 2 || cubin_ready || e.work_seen >= 2e10)) {
             if (!compile_entry(key, &e, smem_bytes)) e.failed = true;
         }
         fn = e.fn;
     }
     if (!fn) return cudaSuccess;
-    const long long tile_px = (long long)threads * pixels_per_thread;
-    const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) { *launched = true; return cudaSuccess; }
-    const long long cap = kind == 0 ? sm_count : 4LL * sm_count;   // the exact kernel's shared tables allow one CTA per SM
-    const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
     void* params[] = {const_cast<LambdaArgs*>(&a), &out64, &out32, &steps};
     const CUresult r = driver().launch_kernel(fn, grid, 1, 1, (unsigned)threads, 1, 1, (unsigned)smem_bytes, (CUstream)st, params, nullptr);
     if (r != CUDA_SUCCESS) {
@@ -249,8 +311,10 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
         g_note = "cuLaunchKernel of the specialised kernel failed";
         g_cache[key].fn = nullptr;
         g_cache[key].failed = true;
-        return cudaSuccess;   // not launched: the caller uses the precompiled kernel
+        return cudaSuccess;   // not launched: the caller uses the generic kernel
     }
+    snprintf(name, sizeof name, "%s_spec<%d px/thread, period %d steps> (compiled at run time)", kinds[kind], pixels_per_thread, 2 * kg);
+    note_lambda_kernel(name);
     *launched = true;
     return cudaSuccess;
 }

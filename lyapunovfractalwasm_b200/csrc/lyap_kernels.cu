@@ -15,6 +15,7 @@
 #include "lyap_math.h"
 
 #include "lyap_exact_kernel.cuh"
+#include "lyap_kernels_fast.cuh"
 
 namespace lyap {
 
@@ -22,34 +23,27 @@ template <int P, int THREADS, bool HAS_C, int UNROLL>
 static cudaError_t launch_exact_variant(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                         int sm_count, cudaStream_t st) {
     auto kern = k_lambda_exact<P, THREADS, HAS_C, UNROLL>;
+    constexpr size_t smem = exact_smem_bytes(THREADS, P);
     // the attribute is per device and cheap to set; doing it on every launch keeps this thread- and device-safe
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kExactSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const long long tile_px = (long long)THREADS * P;
     const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) return cudaSuccess;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    kern<<<grid, THREADS, kExactSmemBytes, st>>>(a, out64, out32, steps);
+    kern<<<grid, THREADS, smem, st>>>(a, out64, out32, steps);
+    static const char* const names[3] = {"k_lambda_exact<2,512> (generic: patterns dispatched every 2 steps)",
+                                         "k_lambda_exact<3,512> (generic: patterns dispatched every 2 steps)",
+                                         "k_lambda_exact<4,512> (generic: patterns dispatched every 2 steps)"};
+    note_lambda_kernel(names[P - 2]);
     return cudaGetLastError();
 }
 
 // Pixels per thread for a launch of n pixels.  Large frames: 3 (measured best on B200).  Small frames are
 // dominated by how many rounds of tiles the busiest SM runs, so the count that minimises rounds * pixels-per-thread
 // (weighted by each shape's measured per-pixel cost) is taken; `spec` says that the 2- and 3-pixel shapes can run as
-// instances compiled for the sequence, which are faster.  LYAP_EXACT_VARIANT=0..4 overrides (tuning knob).
-static int exact_pixels_per_thread(long long n_pixels, int sm_count, int* threads, bool spec) {
-    static const int env = [] {
-        const char* e = getenv("LYAP_EXACT_VARIANT");
-        return e ? atoi(e) : -1;
-    }();
-    *threads = 512;
-    switch (env) {
-        case 0: return 3;
-        case 1: return 2;
-        case 3: return 4;
-        case 4: *threads = 1024; return 2;
-        default: break;
-    }
+// instances compiled for the sequence, which are faster.
+static int exact_pixels_per_thread(long long n_pixels, int sm_count, bool spec) {
     const int cand[3] = {3, 2, 4};
     const double cost[3] = {spec ? 0.92 : 1.0, spec ? 0.95 : 1.035, 1.015};
     int best = 3;
@@ -66,6 +60,16 @@ static int exact_pixels_per_thread(long long n_pixels, int sm_count, int* thread
     return best;
 }
 
+// LYAP_JIT: 0 never compile at run time, 1 (default) once enough work with a sequence has been seen, 2 at once.
+// LYAP_PREBUILT=0: ignore the instances compiled at build time (with LYAP_JIT=0 that forces the generic kernels).
+static int spec_mode() {
+    const char* je = getenv("LYAP_JIT");
+    const char* pe = getenv("LYAP_PREBUILT");
+    const int jit = je ? atoi(je) : 1;
+    const int pre = pe ? atoi(pe) : 1;
+    return (jit < 0 ? 0 : (jit > 2 ? 2 : jit)) | (pre ? kSpecUsePrebuilt : 0);
+}
+
 cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                 int sm_count, cudaStream_t st) {
     bool has_c = false;
@@ -74,22 +78,18 @@ cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32
 #define LYAP_VARIANT(P, T, U)                                                                    \
     (has_c ? launch_exact_variant<P, T, true, U>(a, out64, out32, steps, sm_count, st)            \
            : launch_exact_variant<P, T, false, U>(a, out64, out32, steps, sm_count, st))
-    int threads = 512;
-    // a periodic sequence can run an instance of this kernel compiled for its patterns (LYAP_JIT=0 turns that off,
-    // 2 compiles at once instead of after some work has been seen)
-    const char* je = getenv("LYAP_JIT");
-    const int jit_mode = je ? atoi(je) : 1;
+    // a periodic sequence can run an instance of this kernel made for its patterns
+    const int mode = spec_mode();
     unsigned long long wu_pats = 0, acc_pats = 0;
-    const bool spec = jit_mode > 0 && sequence_group_period(a, &wu_pats, &acc_pats) > 0;
-    const int ppt = exact_pixels_per_thread(a.n_pixels, sm_count, &threads, spec);
-    if (threads == 512 && ppt <= 3) {   // with 4 pixels per thread the specialised instance measured slower
+    const bool spec = mode != 0 && sequence_group_period(a, &wu_pats, &acc_pats) > 0;
+    const int ppt = exact_pixels_per_thread(a.n_pixels, sm_count, spec);
+    if (ppt <= 3) {   // with 4 pixels per thread the specialised instance measured slower
         bool launched = false;
-        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, 0, ppt, 512, kExactSmemBytes, jit_mode,
-                                                 &launched);
+        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, 0, ppt, 512, exact_smem_bytes(512, ppt),
+                                                 mode, &launched);
         if (e != cudaSuccess) return e;
         if (launched) return cudaSuccess;
     }
-    if (threads == 1024) return LYAP_VARIANT(2, 1024, 2);
     if (ppt == 2) return LYAP_VARIANT(2, 512, 2);
     if (ppt == 4) return LYAP_VARIANT(4, 512, 2);
     return LYAP_VARIANT(3, 512, 2);
@@ -183,12 +183,14 @@ k_minmax(const double* __restrict__ v, unsigned long long n, double* __restrict_
     }
 }
 
-cudaError_t launch_minmax(const double* v, unsigned long long n, double* minmax, void* scratch, cudaStream_t st) {
+cudaError_t launch_minmax(const double* v, unsigned long long n, double* minmax, void* scratch, int sm_count, cudaStream_t st) {
     double* partial = static_cast<double*>(scratch);
     unsigned int* ticket = reinterpret_cast<unsigned int*>(partial + 2 * kMinmaxBlocks);
     unsigned long long want = (n / 2 + kMinmaxThreads - 1) / kMinmaxThreads;
     if (want < 1) want = 1;
-    const int grid = (int)(want < (unsigned long long)kMinmaxBlocks ? want : kMinmaxBlocks);
+    // 8 blocks per SM of this device, never more than the scratch has room for
+    const unsigned long long cap = (unsigned long long)(8 * sm_count < kMinmaxBlocks && sm_count > 0 ? 8 * sm_count : kMinmaxBlocks);
+    const int grid = (int)(want < cap ? want : cap);
     k_minmax<<<grid, kMinmaxThreads, 0, st>>>(v, n, minmax, partial, ticket);
     return cudaGetLastError();
 }
@@ -214,30 +216,38 @@ extern "C" int lyap_minmax_device_noalloc(const double* d_values, uint64_t n, do
     if (!d_minmax || (!d_values && n)) return set_error(LYAP_ERR_INVALID, "lyap_minmax_device_noalloc: null pointer");
     if (n > LYAP_NOALLOC_MAX_VALUES)
         return set_error(LYAP_ERR_TOO_LARGE, "lyap_minmax_device_noalloc: n exceeds LYAP_NOALLOC_MAX_VALUES (2^32 values)");
-    constexpr int kMaxDevices = 64;
+    constexpr int kMaxDevices = LYAP_NOALLOC_MAX_DEVICES;
     static std::mutex mu;
     static void* scratch_of_device[kMaxDevices] = {};
+    static int sm_count_of_device[kMaxDevices] = {};
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
-    if (dev < 0 || dev >= kMaxDevices) return set_error(LYAP_ERR_INVALID, "lyap_minmax_device_noalloc: device ordinal out of range");
+    if (dev < 0 || dev >= kMaxDevices)
+        return set_error(LYAP_ERR_INVALID, "lyap_minmax_device_noalloc: device ordinal beyond LYAP_NOALLOC_MAX_DEVICES");
     void* scratch = nullptr;
+    int sm_count = 0;
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!scratch_of_device[dev]) {   // one-time set-up for this device (it is the current one)
             void* p = nullptr;
             e = cudaGetSymbolAddress(&p, g_minmax_fixed_scratch);
             if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
+            int sms = 0;
+            e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
+            sm_count_of_device[dev] = sms;
             scratch_of_device[dev] = p;
         }
         scratch = scratch_of_device[dev];
+        sm_count = sm_count_of_device[dev];
     }
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
     // the arrival ticket must start at zero; the array keeps whatever the last call (or an aborted one) left
     unsigned int* ticket = reinterpret_cast<unsigned int*>(static_cast<double*>(scratch) + 2 * kMinmaxBlocks);
     e = cudaMemsetAsync(ticket, 0, 16, st);
     if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
-    e = launch_minmax(d_values, n, d_minmax, scratch, st);
+    e = launch_minmax(d_values, n, d_minmax, scratch, sm_count, st);
     if (e != cudaSuccess) return set_error(LYAP_ERR_CUDA, cudaGetErrorString(e));
     return LYAP_OK;
 }
@@ -412,11 +422,11 @@ k_colorize(const double* __restrict__ norm, int width, long long rows, int rows_
 }
 
 cudaError_t launch_colorize(const double* norm, int width, long long rows, int rows_above, int rows_below,
-                            int palette, unsigned char* rgba, cudaStream_t st) {
+                            int palette, unsigned char* rgba, int sm_count, cudaStream_t st) {
     const long long n = rows * (long long)width;
     if (n <= 0) return cudaSuccess;
     long long want = (n + kColorThreads - 1) / kColorThreads;
-    const long long cap = 148LL * 64;
+    const long long cap = (long long)sm_count * 64;
     const int grid = (int)(want < cap ? want : cap);
     k_colorize<<<grid, kColorThreads, 0, st>>>(norm, width, rows, rows_above, rows_below, palette,
                                                 reinterpret_cast<unsigned int*>(rgba));
@@ -507,11 +517,12 @@ k_glow_blur_cols_mix(const __grid_constant__ GlowArgs g, unsigned char* __restri
     }
 }
 
-cudaError_t launch_glow(unsigned char* canvas, int width, int height, double* scratch, cudaStream_t st) {
+cudaError_t launch_glow(unsigned char* canvas, int width, int height, double* scratch, int sm_count, cudaStream_t st) {
     const long long n = (long long)width * height;
     if (n <= 0) return cudaSuccess;
     const long long want = (n + kGlowThreads - 1) / kGlowThreads;
-    const int grid = (int)(want < 148LL * 32 ? want : 148LL * 32);
+    const long long cap = (long long)sm_count * 32;
+    const int grid = (int)(want < cap ? want : cap);
     const double sigmas[3] = {6.0, 2.0, 0.0}, alphas[3] = {0.3, 0.4, 0.1};
     for (int pass = 0; pass < 3; ++pass) {
         GlowArgs g{};
@@ -525,10 +536,12 @@ cudaError_t launch_glow(unsigned char* canvas, int width, int height, double* sc
             }
             for (int k = 0; k <= 2 * g.radius; ++k) g.w[k] /= sum;
             k_glow_blur_rows<<<grid, kGlowThreads, 0, st>>>(g, canvas, width, n, scratch);
+            if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
         }
         k_glow_blur_cols_mix<<<grid, kGlowThreads, 0, st>>>(g, canvas, width, height, n, scratch);
+        if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) return e;
     }
-    return cudaGetLastError();
+    return cudaSuccess;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -590,4 +603,42 @@ cudaError_t launch_fp32_peak(float* sink, int sm_count, int iters, unsigned long
 
 }  // namespace lyap
 
-#include "lyap_kernels_fast.cuh"
+namespace lyap {
+
+template <typename T, int P>
+static cudaError_t launch_lambda_fast_t(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                        int sm_count, cudaStream_t st) {
+    {   // a periodic sequence can run an instance made for its patterns (same switches as the exact kernel)
+        bool launched = false;
+        // measured best shapes for the specialised instances: fp64 4 pixels/thread, fp32 2 pixels/thread, 512 threads
+        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, sizeof(T) == 8 ? 1 : 2,
+                                                 sizeof(T) == 8 ? 4 : 2, 512, 0, spec_mode(), &launched);
+        if (e != cudaSuccess) return e;
+        if (launched) return cudaSuccess;
+    }
+    const long long tile_px = (long long)kFastThreads * P;
+    const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
+    if (tiles <= 0) return cudaSuccess;
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_lambda_fast<T, P, kFastThreads>,
+                                                                  kFastThreads, 0);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) per_sm = 1;
+    const long long cap = (long long)sm_count * per_sm;
+    const int grid = (int)(tiles < cap ? tiles : cap);
+    k_lambda_fast<T, P, kFastThreads><<<grid, kFastThreads, 0, st>>>(a, out64, out32, steps);
+    note_lambda_kernel(sizeof(T) == 8 ? "k_lambda_fast<double,4,256> (generic)" : "k_lambda_fast<float,4,256> (generic)");
+    return cudaGetLastError();
+}
+
+cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                 int sm_count, cudaStream_t st) {
+    return launch_lambda_fast_t<double, 4>(a, out64, out32, steps, sm_count, st);
+}
+
+cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                 int sm_count, cudaStream_t st) {
+    return launch_lambda_fast_t<float, 4>(a, out64, out32, steps, sm_count, st);
+}
+
+}  // namespace lyap

@@ -176,7 +176,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
         const long long idx0 = tile * tile_px + (long long)threadIdx.x * P;
         T x[P], prod[P], rA[P], rB[P], rC[P];
         double extra[P], lam[P];
-        int valid[P], esum[P];
+        int valid[P], esum[P];   // 32 bits are enough: the host admits at most 2^24 steps per pixel in the fast modes
         bool done[P], careful_only[P];
         // lambda from the three partial sums: esum*ln2 + log(mantissa product) + terms logged one by one
         auto finish = [&](int e, T m, double ex, int nvalid) -> double {
@@ -377,15 +377,43 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
 #pragma unroll
         for (int p = 0; p < P; ++p)
             if (!done[p]) lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
+        // stores through a staging row in shared memory: 16 bytes per lane, 512 consecutive bytes per warp
+        // (plain stores for a ragged last tile or an output pointer that is not 16-byte aligned)
+        const long long tile0 = tile * tile_px;
+        const bool full_tile = tile0 + tile_px <= a.n_pixels;
+        __shared__ __align__(16) double stage[THREADS * P];
         if (out64) {
+            if (full_tile && ((reinterpret_cast<uintptr_t>(out64 + tile0) & 15) == 0)) {
+                __syncthreads();
 #pragma unroll
-            for (int p = 0; p < P; ++p)
-                if (idx0 + p < a.n_pixels) out64[idx0 + p] = lam[p];
+                for (int p = 0; p < P; ++p) stage[threadIdx.x * P + p] = lam[p];
+                __syncthreads();
+                double2* dst = reinterpret_cast<double2*>(out64 + tile0);
+                const double2* src = reinterpret_cast<const double2*>(stage);
+#pragma unroll
+                for (int i = threadIdx.x; i < THREADS * P / 2; i += THREADS) dst[i] = src[i];
+            } else {
+#pragma unroll
+                for (int p = 0; p < P; ++p)
+                    if (idx0 + p < a.n_pixels) out64[idx0 + p] = lam[p];
+            }
         }
         if (out32) {
+            if (full_tile && ((reinterpret_cast<uintptr_t>(out32 + tile0) & 15) == 0)) {
+                float* stage32 = reinterpret_cast<float*>(stage);
+                __syncthreads();
 #pragma unroll
-            for (int p = 0; p < P; ++p)
-                if (idx0 + p < a.n_pixels) out32[idx0 + p] = (float)lam[p];
+                for (int p = 0; p < P; ++p) stage32[threadIdx.x * P + p] = (float)lam[p];
+                __syncthreads();
+                float4* dst = reinterpret_cast<float4*>(out32 + tile0);
+                const float4* src = reinterpret_cast<const float4*>(stage32);
+#pragma unroll
+                for (int i = threadIdx.x; i < THREADS * P / 4; i += THREADS) dst[i] = src[i];
+            } else {
+#pragma unroll
+                for (int p = 0; p < P; ++p)
+                    if (idx0 + p < a.n_pixels) out32[idx0 + p] = (float)lam[p];
+            }
         }
     }
 
@@ -415,42 +443,5 @@ k_lambda_fast_spec(const __grid_constant__ LambdaArgs a, double* __restrict__ ou
 }
 #endif
 
-#if !defined(__CUDACC_RTC__)
-template <typename T, int P>
-static cudaError_t launch_lambda_fast_t(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
-                                        int sm_count, cudaStream_t st) {
-    {   // a periodic sequence can run an instance compiled for its patterns (same switch as the exact kernel)
-        const char* je = getenv("LYAP_JIT");
-        bool launched = false;
-        // measured best shapes for the specialised instances: fp64 4 pixels/thread, fp32 2 pixels/thread, 512 threads
-        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, sizeof(T) == 8 ? 1 : 2,
-                                                 sizeof(T) == 8 ? 4 : 2, 512, 0, je ? atoi(je) : 1, &launched);
-        if (e != cudaSuccess) return e;
-        if (launched) return cudaSuccess;
-    }
-    const long long tile_px = (long long)kFastThreads * P;
-    const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
-    if (tiles <= 0) return cudaSuccess;
-    int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_lambda_fast<T, P, kFastThreads>,
-                                                                  kFastThreads, 0);
-    if (e != cudaSuccess) return e;
-    if (per_sm < 1) per_sm = 1;
-    const long long cap = (long long)sm_count * per_sm;
-    const int grid = (int)(tiles < cap ? tiles : cap);
-    k_lambda_fast<T, P, kFastThreads><<<grid, kFastThreads, 0, st>>>(a, out64, out32, steps);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
-                                 int sm_count, cudaStream_t st) {
-    return launch_lambda_fast_t<double, 4>(a, out64, out32, steps, sm_count, st);
-}
-
-cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
-                                 int sm_count, cudaStream_t st) {
-    return launch_lambda_fast_t<float, 4>(a, out64, out32, steps, sm_count, st);
-}
-#endif
 
 }  // namespace lyap

@@ -23,7 +23,7 @@
 //     of this restatement against the unmodified reference header built with the same math is
 //     done in tests/test_oracle.py via oracle/_ref.
 //
-// Build: see oracle/Makefile (g++ -O2 -std=c++20 -ffp-contract=off -mfma -fopenmp).
+// Build: see oracle/Makefile (g++ -O3 -std=c++20 -ffp-contract=off -mfma -fopenmp).
 #include <cmath>
 #include <cstdint>
 #include <cstring>

@@ -10,6 +10,9 @@
 #include <cstdint>
 #include <cstring>
 #include <lyapunov_fractal.hpp>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 extern "C" {
 
@@ -32,6 +35,23 @@ int ref_normalize(const double* in, uint64_t n, double* out) {
     std::vector<double> r = lyapunov::normalizeData(v);
     std::memcpy(out, r.data(), r.size() * sizeof(double));
     return (int)r.size();
+}
+
+// Threads the header's "#pragma omp parallel for ... if(params.height > 100)" (src/lyapunov_fractal.hpp:40) will use,
+// and a way to set them (the timed CPU baseline reports a one-thread figure beside the all-threads one).
+int ref_omp_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+void ref_omp_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
 }
 
 // struct defaults (src/lyapunov_fractal.hpp:15-25), for the boundary test

@@ -42,6 +42,29 @@ def engine():
     eng.close()
 
 
+# which lambda kernel a launch takes for a periodic sequence: (LYAP_JIT, LYAP_PREBUILT)
+KERNEL_PATHS = {
+    "generic": ("0", "0"),    # patterns dispatched every two steps at run time
+    "prebuilt": ("0", "1"),   # the instance compiled with the library, where the patterns match one; else generic
+    "jit": ("2", "0"),        # an instance compiled by NVRTC on first use
+}
+
+
+@pytest.fixture()
+def kernel_path():
+    """choose(name) sets the two environment switches the library reads at every launch; restored afterwards."""
+    old = {k: os.environ.get(k) for k in ("LYAP_JIT", "LYAP_PREBUILT")}
+
+    def choose(name):
+        os.environ["LYAP_JIT"], os.environ["LYAP_PREBUILT"] = KERNEL_PATHS[name]
+    yield choose
+    for k, v in old.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
+
+
 # the benchmark configurations 1-4, as make_params keywords (5 is config5_frame below)
 CONFIGS = {
     1: dict(min_x=2.0, max_x=4.0, min_y=2.0, max_y=4.0, width=512, height=512, sequence="AB",

@@ -115,6 +115,15 @@ class Ref:
         L.ref_normalize.restype = ctypes.c_int
         L.ref_normalize.argtypes = [c_double_p, ctypes.c_uint64, c_double_p]
         L.ref_default_params.argtypes = [c_double_p, ctypes.POINTER(ctypes.c_int), ctypes.c_char_p, ctypes.c_int]
+        L.ref_omp_max_threads.restype = ctypes.c_int
+        L.ref_omp_set_threads.argtypes = [ctypes.c_int]
+
+    def max_threads(self):
+        """Threads the header's OpenMP loop uses when it is on (it is off for frames of 100 rows or fewer, :40)."""
+        return int(self.lib.ref_omp_max_threads())
+
+    def set_threads(self, n):
+        self.lib.ref_omp_set_threads(int(n))
 
     def compute_fractal(self, min_x, max_x, min_y, max_y, width, height, sequence, iterations, warmup):
         out = np.empty((height, width), dtype=np.float64)

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_no_compute_calls_needed_for_these():
     lib = L.load_library()
-    assert lib.lyap_abi_version() == 1
+    assert lib.lyap_abi_version() == 2
     assert lib.lyap_self_test() == 42                    # testFunction(), src/wasm_bindings.cpp:19-22
     p = L.LyapParams()
     lib.lyap_params_default(ctypes.byref(p))

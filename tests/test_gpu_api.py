@@ -222,3 +222,127 @@ def test_render_frames_batch_equals_frame_by_frame(engine, port):
     assert "norm" not in out and np.array_equal(out["rgba"][1], engine.render(frames[1], want=("rgba",))["rgba"])
     out, stats = L.render_frames([], [0])
     assert out == {"norm": [], "rgba": []} and stats == []
+
+
+def test_multi_object_gather_and_reuse(engine):
+    """lyap_multi on this device listed three times (NCCL cannot have one GPU twice, so the object takes its host
+    exchange and peer-copy gather; the NCCL legs run where there are distinct devices): the gathered RGBA8 / fp32
+    lambda frames in the first device's memory and every host output equal the one-device render; the object is reused
+    for another frame size and for a frame batch without being rebuilt."""
+    kw = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=301, height=100, sequence="AABAB", iterations=120,
+              warmup=25, palette="nebula")
+    one = engine.render(L.make_params(**kw), want=("lambda", "lambda32", "norm", "rgba"))
+    with L.Multi([0, 0, 0], use_nccl=True) as m:
+        assert "more than once" in m.note()
+        r = m.render(L.make_params(**kw), want=("lambda", "lambda32", "norm", "rgba"),
+                     flags=L.MULTI_GATHER_RGBA | L.MULTI_GATHER_LAMBDA32)
+        st = r["stats"]
+        assert st.used_nccl == 0 and st.gather_bytes == 2 * (100 - 34) * 301 * 4 and st.ms_gather > 0
+        assert np.array_equal(r["lambda"].view(np.uint64), one["lambda"].view(np.uint64))
+        assert np.array_equal(r["lambda32"], one["lambda32"])
+        assert np.array_equal(r["norm"].view(np.uint64), one["norm"].view(np.uint64))
+        assert np.array_equal(r["rgba"], one["rgba"])
+        assert st.executed_steps == one["stats"].executed_steps
+        assert (st.lambda_min, st.lambda_max) == (one["stats"].lambda_min, one["stats"].lambda_max)
+        # the gathered frames themselves, read back from the first device
+        d_rgba, d_l32 = m.gathered()
+        got = np.empty((100, 301, 4), dtype=np.uint8)
+        L._check(engine.lib.lyap_copy_to_host(engine.ctx, got.ctypes.data, d_rgba, got.nbytes))
+        assert np.array_equal(got, one["rgba"])
+        got32 = np.empty((100, 301), dtype=np.float32)
+        L._check(engine.lib.lyap_copy_to_host(engine.ctx, got32.ctypes.data, d_l32, got32.nbytes))
+        assert np.array_equal(got32, one["lambda32"])
+        # gather only (no host buffers), a larger frame, then without gather
+        kw2 = dict(kw, width=640, height=333, sequence="AB", palette="cosmic")
+        one2 = engine.render(L.make_params(**kw2), want=("rgba",))
+        r2 = m.render(L.make_params(**kw2), want=(), flags=L.MULTI_GATHER_RGBA)
+        d_rgba, _ = m.gathered()
+        got = np.empty((333, 640, 4), dtype=np.uint8)
+        L._check(engine.lib.lyap_copy_to_host(engine.ctx, got.ctypes.data, d_rgba, got.nbytes))
+        assert np.array_equal(got, one2["rgba"]) and r2["stats"].gather_bytes == (333 - 111) * 640 * 4
+        r3 = m.render(L.make_params(**kw2), want=("rgba",))
+        assert np.array_equal(r3["rgba"], one2["rgba"]) and r3["stats"].gather_bytes == 0
+        # lambda only: no colour stage, no exchange needed
+        r4 = m.render(L.make_params(**kw), want=("lambda",))
+        assert np.array_equal(r4["lambda"].view(np.uint64), one["lambda"].view(np.uint64))
+        # a batch of frames on the same object
+        frames = [L.make_params(**dict(kw, width=64 + 16 * i, height=40 + i)) for i in range(5)]
+        norms = [np.empty((f.height, f.width)) for f in frames]
+        rgbas = [np.empty((f.height, f.width, 4), dtype=np.uint8) for f in frames]
+        stats = m.render_frames(frames, [a.ctypes.data for a in norms], [a.ctypes.data for a in rgbas])
+        for f, nrm, img, fs in zip(frames, norms, rgbas, stats):
+            ref = engine.render(f, want=("norm", "rgba"))
+            assert np.array_equal(nrm.view(np.uint64), ref["norm"].view(np.uint64)) and np.array_equal(img, ref["rgba"])
+            assert fs.executed_steps == ref["stats"].executed_steps
+
+
+def test_multi_object_single_device_with_nccl(engine):
+    """One device, NCCL asked for: a one-rank communicator; the min/max all-reduce goes through it."""
+    kw = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=200, height=64, sequence="AB", iterations=100, warmup=10)
+    one = engine.render(L.make_params(**kw), want=("norm", "rgba"))
+    with L.Multi([0], use_nccl=True) as m:
+        r = m.render(L.make_params(**kw), want=("norm", "rgba"), flags=L.MULTI_GATHER_RGBA)
+        assert m.note() == "" and r["stats"].used_nccl == 1
+        assert np.array_equal(r["norm"].view(np.uint64), one["norm"].view(np.uint64))
+        assert np.array_equal(r["rgba"], one["rgba"])
+        r = m.render(L.make_params(**kw), want=("rgba",), flags=L.MULTI_HOST_EXCHANGE)
+        assert r["stats"].used_nccl == 0 and np.array_equal(r["rgba"], one["rgba"])
+
+
+def test_multi_object_deadline_and_errors(engine):
+    import time
+    p = L.make_params(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=64, height=32, sequence="AB", iterations=50, warmup=5)
+    with L.Multi([0, -1], use_nccl=True) as m:      # a band that never arrives: no NCCL, the deadline fires on the host
+        assert "no device" in m.note()
+        t0 = time.time()
+        with pytest.raises(L.LyapError) as ei:
+            m.render(p, want=("rgba",), flags=L.MULTI_GATHER_RGBA, timeout_seconds=0.4)
+        assert ei.value.status == 6 and 0.3 < time.time() - t0 < 10
+    with L.Multi([0, 0]) as m:
+        with pytest.raises(L.LyapError) as ei:
+            m.render(L.make_params(width=8, height=8, sequence="", iterations=5, warmup=1))
+        assert ei.value.status == 2
+        with pytest.raises(L.LyapError) as ei:
+            m.render(L.make_params(width=8, height=1, sequence="AB", iterations=5, warmup=1))
+        assert ei.value.status == 1                   # more bands than rows
+        ok = m.render(p, want=("rgba",))               # still usable
+        assert ok["rgba"].shape == (32, 64, 4)
+    with pytest.raises(L.LyapError):
+        L.Multi([9999])
+
+
+def test_drop_in_header_program_runs_and_matches_the_oracle(port, engine, tmp_path):
+    """A program written against the reference's header API (struct, computeFractal with a callback, normalizeData:
+    the calls of src/wasm_bindings.cpp:112-119) compiled against include/lyapunov_fractal.hpp and RUN: its lambda and
+    normalised arrays equal the oracle's."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "user.cpp"
+    src.write_text(
+        '#include "lyapunov_fractal.hpp"\n'
+        "#include <cstdio>\n"
+        "static int calls = 0; static double last = 0;\n"
+        "static void cb(double f) { ++calls; last = f; }\n"
+        "int main(int, char** argv) {\n"
+        "  lyapunov::FractalComputer::ComputationParams params;\n"
+        "  params.min_x = 2.4; params.max_x = 4.0; params.min_y = 2.5; params.max_y = 3.9;\n"
+        '  params.width = 200; params.height = 90; params.sequence = "ABBAB"; params.iterations = 150; params.warmup = 30;\n'
+        "  lyapunov::FractalComputer computer;\n"
+        "  std::vector<double> fractal_data = computer.computeFractal(params, cb);\n"
+        "  std::vector<double> normalized_data = lyapunov::normalizeData(fractal_data);\n"
+        '  FILE* f = std::fopen(argv[1], "wb");\n'
+        "  std::fwrite(fractal_data.data(), 8, fractal_data.size(), f);\n"
+        "  std::fwrite(normalized_data.data(), 8, normalized_data.size(), f);\n"
+        "  std::fclose(f);\n"
+        "  return (calls >= 1 && last == 1.0 && normalized_data.size() == 18000) ? 0 : 1;\n"
+        "}\n")
+    exe, out = tmp_path / "user", tmp_path / "out.bin"
+    libdir = os.path.join(root, "lyapunovfractalwasm_b200")
+    subprocess.run(["g++", "-std=c++23", "-Wall", "-Werror", "-I", os.path.join(root, "include"), str(src),
+                    "-L", libdir, "-llyap_b200", "-Wl,-rpath," + libdir, "-o", str(exe)], check=True)
+    subprocess.run([str(exe), str(out)], check=True)
+    data = np.fromfile(out, dtype=np.float64)
+    lam, _ = port.lambda_rows(2.4, 4.0, 2.5, 3.9, 200, 90, "ABBAB", 150, 30)
+    assert np.array_equal(data[:18000].view(np.uint64), lam.ravel().view(np.uint64))
+    assert np.array_equal(data[18000:].view(np.uint64), port.normalize(lam).ravel().view(np.uint64))

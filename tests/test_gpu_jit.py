@@ -1,5 +1,6 @@
-"""The run-time specialised instance of the exact kernel (csrc/lyap_jit.cu) against the CPU oracle and against the
-precompiled kernel: same bits, same executed-step counts.  LYAP_JIT=2 compiles on first use, 0 turns it off."""
+"""The instances of the lambda kernels made for one sequence -- compiled with the library (csrc/lyap_prebuilt.cu) or at
+run time (csrc/lyap_jit.cu) -- against the CPU oracle and against the generic kernel: same bits, same executed-step
+counts.  The kernel_path fixture picks which of the three a launch takes."""
 import os
 
 import numpy as np
@@ -9,19 +10,6 @@ import lyapunovfractalwasm_b200 as L
 from conftest import CONFIGS, config5_frame
 
 pytestmark = pytest.mark.gpu
-
-
-@pytest.fixture()
-def jit_mode():
-    old = os.environ.get("LYAP_JIT")
-
-    def set_mode(m):
-        os.environ["LYAP_JIT"] = str(m)
-    yield set_mode
-    if old is None:
-        os.environ.pop("LYAP_JIT", None)
-    else:
-        os.environ["LYAP_JIT"] = old
 
 
 def oracle(port, kw):
@@ -43,44 +31,77 @@ CASES = [
 
 
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "%s_%d_%d" % (c["sequence"][:12], c["iterations"], c["warmup"]))
-def test_specialised_kernel_is_bit_exact(engine, port, jit_mode, case):
+def test_specialised_kernel_is_bit_exact(engine, port, kernel_path, case):
     kw = dict(min_x=2.3, max_x=4.1, min_y=2.2, max_y=4.05, width=333, height=67, **case)
     want, steps = oracle(port, kw)
     got = {}
-    for mode in (2, 0):
-        jit_mode(mode)
+    names = {}
+    for mode in ("jit", "prebuilt", "generic"):
+        kernel_path(mode)
         r = engine.render(L.make_params(**kw), want=("lambda",))
         assert np.array_equal(r["lambda"].view(np.uint64), want.view(np.uint64)), mode
         assert r["stats"].executed_steps == steps, mode
         got[mode] = r["lambda"]
-    assert np.array_equal(got[0].view(np.uint64), got[2].view(np.uint64))
+        names[mode] = engine.lib.lyap_last_kernel().decode()
+    assert np.array_equal(got["generic"].view(np.uint64), got["jit"].view(np.uint64))
     assert engine.lib.lyap_jit_note() == b""      # nothing fell back
+    assert "generic" in names["generic"]
+    periodic = len(case["sequence"]) <= 12
+    assert ("compiled at run time" in names["jit"]) == periodic, names
+    if case == CASES[0]:
+        assert "built for the patterns" in names["prebuilt"], names
 
 
-def test_specialised_kernel_on_the_page_call_with_mid_run_exits(engine, port, jit_mode):
-    jit_mode(2)
+def test_specialised_kernel_on_the_page_call_with_mid_run_exits(engine, port, kernel_path):
     kw = dict(min_x=0.0, max_x=4.0, min_y=0.0, max_y=4.0, width=800, height=800, sequence="AB", iterations=1000, warmup=100)
-    r = engine.render(L.make_params(**kw), want=("lambda",))
     want, steps = oracle(port, kw)
-    assert np.array_equal(r["lambda"].view(np.uint64), want.view(np.uint64)) and r["stats"].executed_steps == steps
+    for mode in ("jit", "prebuilt"):
+        kernel_path(mode)
+        r = engine.render(L.make_params(**kw), want=("lambda",))
+        assert np.array_equal(r["lambda"].view(np.uint64), want.view(np.uint64)) and r["stats"].executed_steps == steps, mode
+        assert "generic" not in engine.lib.lyap_last_kernel().decode()
 
 
-def test_specialised_kernel_on_benchmark_shapes(engine, port, jit_mode):
-    jit_mode(2)
-    kw = CONFIGS[2]
-    lam = engine.compute_fractal(L.make_params(**kw, row_begin=1000, row_end=1016))
-    want, _ = port.lambda_rows(kw["min_x"], kw["max_x"], kw["min_y"], kw["max_y"], kw["width"], kw["height"],
-                               kw["sequence"], kw["iterations"], kw["warmup"], y0=1000, y1=1016)
-    assert np.array_equal(lam.view(np.uint64), want.view(np.uint64))
-    kw = config5_frame(3)
-    lam = engine.compute_fractal(L.make_params(**kw, row_begin=100, row_end=108))
-    want, _ = port.lambda_rows(kw["min_x"], kw["max_x"], kw["min_y"], kw["max_y"], kw["width"], kw["height"],
-                               kw["sequence"], kw["iterations"], kw["warmup"], c=kw["c"], y0=100, y1=108)
-    assert np.array_equal(lam.view(np.uint64), want.view(np.uint64))
+def test_every_benchmark_sequence_has_a_prebuilt_instance(engine, port, kernel_path):
+    """Bands of the five benchmark frames (and "ABC" without the third parameter): the library's own instance for the
+    sequence is what launches -- no run-time compiler involved -- and it gives the oracle's bits; so does NVRTC's."""
+    shapes = [(CONFIGS[1], 100, 140), (CONFIGS[2], 1000, 1016), (CONFIGS[3], 9000, 9004), (CONFIGS[4], 40000, 40001),
+              (config5_frame(3), 100, 108), (dict(config5_frame(3), c=None), 100, 108)]
+    for kw, y0, y1 in shapes:
+        kw = dict(kw)
+        c = kw.pop("c", None)
+        want, _ = port.lambda_rows(kw["min_x"], kw["max_x"], kw["min_y"], kw["max_y"], kw["width"], kw["height"],
+                                   kw["sequence"], kw["iterations"], kw["warmup"], c=c, y0=y0, y1=y1)
+        for mode in ("prebuilt", "jit"):
+            kernel_path(mode)
+            lam = engine.compute_fractal(L.make_params(**kw, c=c, row_begin=y0, row_end=y1))
+            assert np.array_equal(lam.view(np.uint64), want.view(np.uint64)), (kw["sequence"], mode)
+            name = engine.lib.lyap_last_kernel().decode()
+            assert ("built for the patterns" in name) == (mode == "prebuilt"), (kw["sequence"], mode, name)
+        for fast in (L.MODE_FAST_FP64, L.MODE_FAST_FP32):
+            kernel_path("prebuilt")
+            engine.render(L.make_params(**kw, c=c, row_begin=y0, row_end=y1, mode=fast), want=("lambda",))
+            assert "built for the patterns" in engine.lib.lyap_last_kernel().decode(), (kw["sequence"], fast)
+
+
+def test_no_warmup_many_small_launches(engine, port, kernel_path):
+    """warmup = 0: the first logarithm comes right after the kernel has filled its shared-memory tables, so a missing
+    barrier between the fill and the first look-up would show here.  Many small launches, every kernel path."""
+    rng = np.random.default_rng(5)
+    shapes = [(int(rng.integers(1, 2000)), int(rng.integers(1, 5))) for _ in range(40)] + [(1536, 148), (4096, 37)]
+    for seq in ("AB", "AABAB"):
+        for mode in ("generic", "prebuilt", "jit"):
+            kernel_path(mode)
+            for w, h in shapes:
+                kw = dict(min_x=2.5, max_x=3.99, min_y=2.6, max_y=3.97, width=w, height=h, sequence=seq, iterations=24, warmup=0)
+                r = engine.render(L.make_params(**kw), want=("lambda",))
+                want, steps = oracle(port, kw)
+                assert np.array_equal(r["lambda"].view(np.uint64), want.view(np.uint64)), (seq, mode, w, h)
+                assert r["stats"].executed_steps == steps
 
 
 @pytest.mark.parametrize("mode", [L.MODE_FAST_FP64, L.MODE_FAST_FP32])
-def test_specialised_fast_kernels_agree_with_the_precompiled_ones(engine, jit_mode, mode):
+def test_specialised_fast_kernels_agree_with_the_precompiled_ones(engine, kernel_path, mode):
     """Fast modes: moving the exponent out of the running product is exact, so where the products are stripped does
     not change their value: pixels whose run was regular get the precompiled kernel's bits.  Pixels that had a chunk
     redone step by step (an exit, a zero derivative) may differ in the last digits, because the two kernels cut the
@@ -89,15 +110,16 @@ def test_specialised_fast_kernels_agree_with_the_precompiled_ones(engine, jit_mo
     for case in CASES[:6]:
         kw = dict(min_x=2.3, max_x=4.1, min_y=2.2, max_y=4.05, width=257, height=45, mode=mode, **case)
         got = {}
-        for m in (2, 0):
-            jit_mode(m)
+        for m in ("jit", "prebuilt", "generic"):
+            kernel_path(m)
             r = engine.render(L.make_params(**kw), want=("lambda",))
             got[m] = (r["lambda"], r["stats"].executed_steps)
-        same = got[0][0].view(np.uint64) == got[2][0].view(np.uint64)
-        assert same.mean() > 0.9, (case, same.mean())
-        assert np.array_equal(got[0][0] == -5.0, got[2][0] == -5.0)
-        assert np.max(np.abs(got[0][0] - got[2][0])) < tol, case
-        assert got[0][1] == got[2][1], case
+        for m in ("jit", "prebuilt"):
+            same = got["generic"][0].view(np.uint64) == got[m][0].view(np.uint64)
+            assert same.mean() > 0.9, (case, m, same.mean())
+            assert np.array_equal(got["generic"][0] == -5.0, got[m][0] == -5.0)
+            assert np.max(np.abs(got["generic"][0] - got[m][0])) < tol, (case, m)
+            assert got["generic"][1] == got[m][1], (case, m)
     assert engine.lib.lyap_jit_note() == b""
 
 
@@ -112,12 +134,12 @@ LONG_RUNS = [
 
 
 @pytest.mark.parametrize("case", LONG_RUNS, ids=lambda c: "%d_%d_%d" % (len(c["sequence"]), c["iterations"], c["warmup"]))
-def test_runs_longer_than_the_selector_table(engine, port, jit_mode, case):
+def test_runs_longer_than_the_selector_table(engine, port, kernel_path, case):
     """Specialised and precompiled kernels, exact mode, bit for bit; the fast modes on the same frame to their tolerance."""
     kw = dict(min_x=2.4, max_x=4.0, min_y=2.4, max_y=4.0, width=50, height=21, **case)
     want, steps = oracle(port, kw)
-    for mode in (2, 0):
-        jit_mode(mode)
+    for mode in ("jit", "generic"):
+        kernel_path(mode)
         r = engine.render(L.make_params(**kw), want=("lambda",))
         assert np.array_equal(r["lambda"].view(np.uint64), want.view(np.uint64)), mode
         assert r["stats"].executed_steps == steps, mode

@@ -187,30 +187,22 @@ def test_extreme_parameters(engine, port):
         assert same_bits(got["lambda"], want) and got["stats"].executed_steps == steps, win
 
 
-def test_seeded_random_cases_against_the_oracle(engine, port):
+def test_seeded_random_cases_against_the_oracle(engine, port, kernel_path):
     """40 seeded draws of window, shape, sequence (letters A, B, C and a stray byte), step counts and the optional c:
     lambda bits, executed steps, normalised bits and RGBA bytes, with the run-time specialised kernels on and off."""
-    import os
     rng = np.random.default_rng(20240607)
-    old = os.environ.get("LYAP_JIT")
-    try:
-        for case in range(40):
-            lo_x, lo_y = rng.uniform(-0.2, 3.6, size=2)
-            kw = dict(min_x=float(lo_x), max_x=float(lo_x + rng.uniform(0.05, 4.3 - lo_x)),
-                      min_y=float(lo_y), max_y=float(lo_y + rng.uniform(0.05, 4.3 - lo_y)),
-                      width=int(rng.integers(1, 300)), height=int(rng.integers(1, 60)),
-                      sequence="".join(rng.choice(list("AABBCx"), size=int(rng.integers(1, 40)))),
-                      iterations=int(rng.integers(0, 700)), warmup=int(rng.integers(0, 150)))
-            if rng.random() < 0.5:
-                kw["c"] = float(rng.uniform(0.5, 4.1))
-            os.environ["LYAP_JIT"] = "2" if case % 2 else "0"
-            r = engine.render(L.make_params(**kw, palette=case % 7), want=("lambda", "norm", "rgba"))
-            lam, steps = oracle_rows(port, kw)
-            assert same_bits(r["lambda"], lam) and r["stats"].executed_steps == steps, kw
-            norm = port.normalize(lam)
-            assert same_bits(r["norm"], norm) and np.array_equal(r["rgba"], port.colorize(norm, case % 7)), kw
-    finally:
-        if old is None:
-            os.environ.pop("LYAP_JIT", None)
-        else:
-            os.environ["LYAP_JIT"] = old
+    for case in range(40):
+        lo_x, lo_y = rng.uniform(-0.2, 3.6, size=2)
+        kw = dict(min_x=float(lo_x), max_x=float(lo_x + rng.uniform(0.05, 4.3 - lo_x)),
+                  min_y=float(lo_y), max_y=float(lo_y + rng.uniform(0.05, 4.3 - lo_y)),
+                  width=int(rng.integers(1, 300)), height=int(rng.integers(1, 60)),
+                  sequence="".join(rng.choice(list("AABBCx"), size=int(rng.integers(1, 40)))),
+                  iterations=int(rng.integers(0, 700)), warmup=int(rng.integers(0, 150)))
+        if rng.random() < 0.5:
+            kw["c"] = float(rng.uniform(0.5, 4.1))
+        kernel_path("jit" if case % 2 else "generic")
+        r = engine.render(L.make_params(**kw, palette=case % 7), want=("lambda", "norm", "rgba"))
+        lam, steps = oracle_rows(port, kw)
+        assert same_bits(r["lambda"], lam) and r["stats"].executed_steps == steps, kw
+        norm = port.normalize(lam)
+        assert same_bits(r["norm"], norm) and np.array_equal(r["rgba"], port.colorize(norm, case % 7)), kw

@@ -79,3 +79,30 @@ def test_noalloc_rejects_oversize_and_null(engine):
     assert lib.lyap_minmax_device_noalloc(out.ptr, 10, None, None) == 1
     assert lib.lyap_minmax_device_noalloc(None, 10, out.ptr, None) == 1
     out.free()
+
+
+def test_noalloc_on_a_caller_stream_two_calls_in_order(engine):
+    """The documented use: the caller's own (non-blocking) stream, two calls back to back on it with nothing in
+    between -- the second starts from the scratch the first left -- then one wait for the stream."""
+    cudart = ctypes.CDLL("libcudart.so.12")
+    stream = ctypes.c_void_p()
+    assert cudart.cudaStreamCreateWithFlags(ctypes.byref(stream), 1) == 0      # cudaStreamNonBlocking
+    rng = np.random.default_rng(99)
+    n1, n2 = 1_200_007, 333_331
+    v = rng.uniform(-7.0, 1.5, size=n1 + n2)
+    v[::53] = -5.0
+    buf = engine.alloc(8 * (n1 + n2))
+    buf.from_host(v)
+    want1, want2, got1, got2 = (engine.alloc(16) for _ in range(4))
+    w1 = reference_minmax(engine, buf, 0, n1, want1).copy()
+    w2 = reference_minmax(engine, buf, n1, n2, want2).copy()
+    engine.sync()
+    L.minmax_device_noalloc(buf.ptr, n1, got1.ptr, stream)
+    L.minmax_device_noalloc(buf.ptr + 8 * n1, n2, got2.ptr, stream)
+    assert cudart.cudaStreamSynchronize(stream) == 0
+    g1, g2 = got1.to_host(np.float64), got2.to_host(np.float64)
+    assert np.array_equal(g1.view(np.uint64), w1.view(np.uint64))
+    assert np.array_equal(g2.view(np.uint64), w2.view(np.uint64))
+    assert cudart.cudaStreamDestroy(stream) == 0
+    for b in (buf, want1, want2, got1, got2):
+        b.free()
