@@ -185,7 +185,8 @@ const char* lyap_multi_note(lyap_multi* m);
 enum lyap_multi_flags {
     LYAP_MULTI_GATHER_RGBA = 1,      /* collect every band's RGBA8 in the first device's own frame buffer */
     LYAP_MULTI_GATHER_LAMBDA32 = 2,  /* likewise the (float)lambda bands */
-    LYAP_MULTI_HOST_EXCHANGE = 4     /* frame min/max through the host even when NCCL is available */
+    LYAP_MULTI_HOST_EXCHANGE = 4     /* this call without NCCL even where it is available: frame min/max through the
+                                        host, a gather by peer copies (cudaMemcpyPeerAsync) */
 };
 
 typedef struct lyap_multi_stats {

@@ -561,8 +561,8 @@ int lyap_multi_create(lyap_multi** out, int32_t n_devices, const int32_t* device
         }
     }
     nccl_setup(m);   // a failure here is not fatal: the object then works through the host (see lyap_multi_note)
-    if (!m->nccl_ready && m->slots[0].device >= 0) {
-        // the gather then uses peer copies into the first device: let them go over NVLink instead of through the host
+    if (m->slots[0].device >= 0) {
+        // a gather without NCCL uses peer copies into the first device: let them go over NVLink instead of through the host
         for (int i = 1; i < n_devices; ++i) {
             const int d = m->slots[i].device;
             int can = 0;

@@ -346,3 +346,52 @@ def test_drop_in_header_program_runs_and_matches_the_oracle(port, engine, tmp_pa
     lam, _ = port.lambda_rows(2.4, 4.0, 2.5, 3.9, 200, 90, "ABBAB", 150, 30)
     assert np.array_equal(data[:18000].view(np.uint64), lam.ravel().view(np.uint64))
     assert np.array_equal(data[18000:].view(np.uint64), port.normalize(lam).ravel().view(np.uint64))
+
+
+def device_count(lib):
+    n = ctypes.c_int(0)
+    lib.lyap_device_count(ctypes.byref(n))
+    return n.value
+
+
+def test_multi_object_on_distinct_devices_with_nccl(engine):
+    """Needs two or more GPUs (skipped on a one-GPU box): every device its own band, the frame's min/max by one NCCL
+    all-reduce, the RGBA8 and fp32 lambda bands gathered into device 0 by ncclSend / grouped ncclRecv.  The bytes equal
+    the one-device render, the host-assembled frame (no gather, host exchange) and the peer-copy gather."""
+    n = device_count(engine.lib)
+    if n < 2:
+        pytest.skip("one GPU here")
+    n = min(n, 8)
+    kw = dict(min_x=2.5, max_x=4.0, min_y=2.5, max_y=4.0, width=1500, height=1003, sequence="AABAB", iterations=300,
+              warmup=40, palette="aurora")
+    one = engine.render(L.make_params(**kw), want=("lambda", "lambda32", "norm", "rgba"))
+    with L.Multi(list(range(n)), use_nccl=True) as m:
+        assert m.note() == ""
+        for _ in range(2):     # second pass: warm connections, reused buffers
+            r = m.render(L.make_params(**kw), want=("lambda", "lambda32", "norm", "rgba"),
+                         flags=L.MULTI_GATHER_RGBA | L.MULTI_GATHER_LAMBDA32)
+            st = r["stats"]
+            assert st.used_nccl == 1 and st.ms_gather > 0
+            own0 = 1003 // n + (1 if 1003 % n else 0)
+            assert st.gather_bytes == 2 * (1003 - own0) * 1500 * 4
+            assert np.array_equal(r["lambda"].view(np.uint64), one["lambda"].view(np.uint64))
+            assert np.array_equal(r["lambda32"], one["lambda32"])
+            assert np.array_equal(r["norm"].view(np.uint64), one["norm"].view(np.uint64))
+            assert np.array_equal(r["rgba"], one["rgba"])
+            assert st.executed_steps == one["stats"].executed_steps
+            assert (st.lambda_min, st.lambda_max) == (one["stats"].lambda_min, one["stats"].lambda_max)
+        host = m.render(L.make_params(**kw), want=("norm", "rgba"), flags=L.MULTI_HOST_EXCHANGE)
+        assert host["stats"].used_nccl == 0 and host["stats"].gather_bytes == 0
+        assert np.array_equal(host["rgba"], one["rgba"]) and np.array_equal(host["norm"].view(np.uint64), one["norm"].view(np.uint64))
+        peer = m.render(L.make_params(**kw), want=("rgba",), flags=L.MULTI_HOST_EXCHANGE | L.MULTI_GATHER_RGBA)
+        assert peer["stats"].used_nccl == 0 and peer["stats"].gather_bytes == (1003 - own0) * 1500 * 4
+        assert np.array_equal(peer["rgba"], one["rgba"])
+        # frames of a batch dealt to distinct devices
+        frames = [L.make_params(**dict(kw, width=200 + 8 * i, height=120 + i, iterations=100)) for i in range(2 * n + 1)]
+        rgbas = [np.empty((f.height, f.width, 4), dtype=np.uint8) for f in frames]
+        m.render_frames(frames, None, [a.ctypes.data for a in rgbas])
+        for f, img in zip(frames, rgbas):
+            assert np.array_equal(img, engine.render(f, want=("rgba",))["rgba"])
+    # the one-call form over distinct devices
+    multi = L.render_multi(L.make_params(**kw), list(range(n)))
+    assert np.array_equal(multi["rgba"], one["rgba"]) and np.array_equal(multi["lambda"].view(np.uint64), one["lambda"].view(np.uint64))

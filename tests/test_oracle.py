@@ -134,3 +134,63 @@ def test_box_mean_counts(port):
     assert b[0, 0] == (0 + 1 + 4 + 5) / 4 and b[1, 1] == np.sum(v[0:3, 0:3]) / 9 and b[0, 1] == (1 + 0 + 2 + 4 + 5 + 6) / 6
     one = port.box3(np.array([[0.75]]))
     assert one[0, 0] == 0.75
+
+
+def ulp_distance(a, b):
+    """Number of representable doubles between a and b (elementwise), for finite values."""
+    ia = np.ascontiguousarray(a).view(np.int64).astype(np.int64)
+    ib = np.ascontiguousarray(b).view(np.int64).astype(np.int64)
+    ia = np.where(ia < 0, np.int64(-2 ** 63) - ia, ia)      # two's-complement order -> numeric order
+    ib = np.where(ib < 0, np.int64(-2 ** 63) - ib, ib)
+    return np.abs(ia - ib)
+
+
+LIBM_DISTANCE_FRAMES = {
+    # name: (min_x, max_x, min_y, max_y, width, height, sequence, iterations, warmup)
+    "cfg1 512x512 AB 100+1000": (2.0, 4.0, 2.0, 4.0, 512, 512, "AB", 1000, 100),
+    "cfg2 window at 768x768 AABAB 200+2000": (2.5, 4.0, 2.5, 4.0, 768, 768, "AABAB", 2000, 200),
+    "cfg3 window at 512x512 B6A6 500+4000": (3.4, 4.0, 2.5, 3.4, 512, 512, "BBBBBBAAAAAA", 4000, 500),
+    "page call 800x800 [0,4]^2 AB 100+1000": (0.0, 4.0, 0.0, 4.0, 800, 800, "AB", 1000, 100),
+    "cfg5 frame 100 at 960x540 ABC (no c) 300+3000": (3.82 - 0.5 * 0.97 ** 100, 3.82 + 0.5 * 0.97 ** 100,
+                                                      3.45 - 0.5 * 0.97 ** 100, 3.45 + 0.5 * 0.97 ** 100, 960, 540, "ABC", 3000, 300),
+}
+
+
+def libm_distance(port, stock, mine, args):
+    a, b = stock.compute_fractal(*args), mine.compute_fractal(*args)
+    na, nb = stock.normalize(a), mine.normalize(b)
+    differ = a != b
+    ulps = ulp_distance(a[differ], b[differ]) if differ.any() else np.zeros(1, dtype=np.int64)
+    rel = np.abs(a[differ] - b[differ]) / np.maximum(np.abs(b[differ]), 1e-300) if differ.any() else np.zeros(1)
+    ra, rb = port.colorize(na), port.colorize(nb)
+    return {"pixels": a.size, "sentinels_equal": bool(np.array_equal(a == -5.0, b == -5.0)),
+            "lambda_differ": int(differ.sum()), "lambda_max_ulp": int(ulps.max()), "lambda_max_rel": float(rel.max()),
+            "lambda_max_abs": float(np.max(np.abs(a - b))),
+            "norm_differ": int((na != nb).sum()), "norm_max_abs": float(np.max(np.abs(na - nb))),
+            "rgba_bytes_differ": int((ra != rb).sum())}
+
+
+def test_distance_to_the_host_libm_build_on_every_frame_shape(port):
+    """The reference header linked to the host libm against the same header linked to this project's math, on the
+    shapes of the benchmark frames: the sentinels are the same pixels, lambda agrees to 1e-12 relative or 1e-13 absolute
+    (the log values differ in their last bit, the sums a little more where they cancel near lambda = 0), and NOT ONE
+    RGBA BYTE differs.  `python tests/test_oracle.py` prints the table."""
+    stock, mine = O.ref("stock"), O.ref("lyapmath")
+    if stock is None:
+        pytest.skip("oracle/_ref not present")
+    for name, args in LIBM_DISTANCE_FRAMES.items():
+        d = libm_distance(port, stock, mine, args)
+        assert d["sentinels_equal"], name
+        assert d["lambda_max_abs"] <= 1e-12 and d["norm_max_abs"] < 1e-12, (name, d)
+        assert d["rgba_bytes_differ"] == 0, (name, d)
+
+
+if __name__ == "__main__":
+    _port, _stock, _mine = O.port(), O.ref("stock"), O.ref("lyapmath")
+    print("| frame | pixels | lambda values that differ | largest difference (ulp / relative / absolute) | normalised values that differ (largest) | RGBA bytes that differ |")
+    print("|---|---|---|---|---|---|")
+    for _name, _args in LIBM_DISTANCE_FRAMES.items():
+        _d = libm_distance(_port, _stock, _mine, _args)
+        print("| %s | %d | %d | %d / %.1e / %.1e | %d (%.1e) | %d |" % (
+            _name, _d["pixels"], _d["lambda_differ"], _d["lambda_max_ulp"], _d["lambda_max_rel"], _d["lambda_max_abs"],
+            _d["norm_differ"], _d["norm_max_abs"], _d["rgba_bytes_differ"]))
