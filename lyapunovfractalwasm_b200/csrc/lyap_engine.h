@@ -31,12 +31,14 @@ const char* jit_last_note();
 const char* last_lambda_kernel();
 void note_lambda_kernel(const char* text);
 
-// A lambda kernel compiled at build time for one sequence's patterns (lyap_prebuilt.cu).  kind: 0 exact, 1 fast fp64,
-// 2 fast fp32.  launch_lambda_spec prefers a matching entry to compiling one at run time.
+// A lambda kernel compiled at build time for one sequence's patterns: device code (a cubin for sm_100a) embedded in the
+// library, made by build.py with the same compiler, source text and options as a run-time instance (lyap_prebuilt.cu).
+// kind: 0 exact, 1 fast fp64, 2 fast fp32.  launch_lambda_spec prefers a matching entry to compiling at run time.
 struct PrebuiltKernel {
     int kind, pixels_per_thread, threads, kg;
     unsigned long long wu_pats, acc_pats;
-    const void* fn;
+    const unsigned char* cubin;
+    size_t cubin_bytes;
     const char* sequence;
 };
 void register_prebuilt(const PrebuiltKernel& k);

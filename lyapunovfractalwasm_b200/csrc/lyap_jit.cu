@@ -98,7 +98,8 @@ Driver& driver() {
     return d;
 }
 
-using Key = std::tuple<int, int, int, unsigned long long, unsigned long long, int, int>;   // device, P, KG, warm-up pats, acc pats, kind, threads
+// device, P, KG, warm-up pats, acc pats, kind, threads, origin (0: compiled at run time, 1: embedded at build time)
+using Key = std::tuple<int, int, int, unsigned long long, unsigned long long, int, int, int>;
 
 struct Entry {
     CUfunction fn = nullptr;
@@ -108,7 +109,7 @@ struct Entry {
 
 std::map<Key, Entry> g_cache;
 // compiled code does not depend on the device ordinal: one compilation serves every GPU of the process
-using CodeKey = std::tuple<int, int, unsigned long long, unsigned long long, int, int>;   // Key without the device
+using CodeKey = std::tuple<int, int, unsigned long long, unsigned long long, int, int, int>;   // Key without the device
 std::map<CodeKey, std::vector<char>> g_cubins;
 
 // NVRTC: source text + pattern macros -> cubin for sm_100a.
@@ -125,7 +126,8 @@ bool compile_cubin(const Key& key, std::vector<char>* out) {
     snprintf(o_kg, sizeof o_kg, "-DLYAP_SPEC_KG=%d", std::get<2>(key));
     snprintf(o_wu, sizeof o_wu, "-DLYAP_SPEC_WU_PATS=0x%llxull", std::get<3>(key));
     snprintf(o_acc, sizeof o_acc, "-DLYAP_SPEC_ACC_PATS=0x%llxull", std::get<4>(key));
-    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", o_thr, o_kind,
+    // build.py compiles the embedded instances with exactly these options (keep the two lists the same)
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", "-lineinfo", o_thr, o_kind,
                           o_p, o_kg, o_wu, o_acc};
     const char* header_src[] = {kSrc_lyap_exact_kernel_cuh, kSrc_lyap_kernels_fast_cuh, kSrc_lyap_args_h, kSrc_lyap_math_h,
                                 kSrc_lyap_tables_h};
@@ -159,12 +161,14 @@ bool compile_cubin(const Key& key, std::vector<char>* out) {
 }
 
 // Loads the (cached) cubin into the current device's context and looks the kernel up.
-bool compile_entry(const Key& key, Entry* e, size_t smem_bytes) {
+bool compile_entry(const Key& key, Entry* e, size_t smem_bytes, const PrebuiltKernel* embedded = nullptr) {
     Driver& d = driver();
     if (!d.ok) { g_note = "driver entry points not available"; return false; }
     const int kind = std::get<5>(key);
-    const CodeKey ck{std::get<1>(key), std::get<2>(key), std::get<3>(key), std::get<4>(key), kind, std::get<6>(key)};
+    const CodeKey ck{std::get<1>(key), std::get<2>(key), std::get<3>(key), std::get<4>(key), kind, std::get<6>(key), std::get<7>(key)};
     std::vector<char>& cubin = g_cubins[ck];
+    if (cubin.empty() && embedded) cubin.assign(reinterpret_cast<const char*>(embedded->cubin),
+                                                reinterpret_cast<const char*>(embedded->cubin) + embedded->cubin_bytes);
     if (cubin.empty() && !compile_cubin(key, &cubin)) {
         cubin.clear();
         return false;
@@ -256,6 +260,11 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
     char name[160];
     static const char* const kinds[3] = {"k_lambda_exact", "k_lambda_fast<double>", "k_lambda_fast<float>"};
 
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return ce;
+    void* params[] = {const_cast<LambdaArgs*>(&a), &out64, &out32, &steps};
+
     if (mode & kSpecUsePrebuilt) {   // an instance compiled with the library
         for (const PrebuiltKernel& k : prebuilt_list()) {
             // a region shorter than one period never runs its straight-line block (it is walked step by step from the
@@ -265,16 +274,26 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
             if (k.kind != kind || k.pixels_per_thread != pixels_per_thread || k.threads != threads || k.kg != kg ||
                 (a.warmup >= bs && k.wu_pats != wu) || (a.iterations >= bs && k.acc_pats != acc) || uses_c != k_uses_c)
                 continue;
-            if (tiles > 0) {
-                if (smem_bytes) {
-                    const cudaError_t ae = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-                    if (ae != cudaSuccess) return ae;
-                }
-                void* params[] = {const_cast<LambdaArgs*>(&a), &out64, &out32, &steps};
-                const cudaError_t le = cudaLaunchKernel(k.fn, dim3(grid), dim3((unsigned)threads), params, smem_bytes, st);
-                if (le != cudaSuccess) return le;
+            const Key key{dev, pixels_per_thread, kg, k.wu_pats, k.acc_pats, kind, threads, 1};
+            CUfunction fn = nullptr;
+            {
+                std::lock_guard<std::mutex> lk(g_mu);
+                Entry& e = g_cache[key];
+                if (!e.fn && !e.failed && !compile_entry(key, &e, smem_bytes, &k)) e.failed = true;   // loads the embedded code
+                fn = e.fn;
             }
-            snprintf(name, sizeof name, "%s_seq<%d px/thread, period %d steps> (built for the patterns of \"%s\")", kinds[kind],
+            if (!fn) break;   // could not be loaded (lyap_jit_note says why): run-time compilation or the generic kernel
+            if (tiles > 0) {
+                const CUresult r = driver().launch_kernel(fn, grid, 1, 1, (unsigned)threads, 1, 1, (unsigned)smem_bytes, (CUstream)st, params, nullptr);
+                if (r != CUDA_SUCCESS) {
+                    std::lock_guard<std::mutex> lk(g_mu);
+                    g_note = "cuLaunchKernel of the embedded kernel failed";
+                    g_cache[key].fn = nullptr;
+                    g_cache[key].failed = true;
+                    break;
+                }
+            }
+            snprintf(name, sizeof name, "%s_spec<%d px/thread, period %d steps> (built for the patterns of \"%s\")", kinds[kind],
                      pixels_per_thread, 2 * kg, k.sequence);
             note_lambda_kernel(name);
             *launched = true;
@@ -283,10 +302,7 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
     }
     if (jit_mode == 0) return cudaSuccess;
 
-    int dev = 0;
-    cudaError_t ce = cudaGetDevice(&dev);
-    if (ce != cudaSuccess) return ce;
-    const Key key{dev, pixels_per_thread, kg, wu, acc, kind, threads};
+    const Key key{dev, pixels_per_thread, kg, wu, acc, kind, threads, 0};
     CUfunction fn = nullptr;
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -294,7 +310,7 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
         e.work_seen += (double)a.n_pixels * ((double)a.warmup + a.iterations);
         // compiling takes about a second, so it waits until that much work with these patterns has been asked for;
         // code another device of this process already compiled is only loaded, which is cheap
-        const CodeKey ck{pixels_per_thread, kg, wu, acc, kind, threads};
+        const CodeKey ck{pixels_per_thread, kg, wu, acc, kind, threads, 0};
         const auto have = g_cubins.find(ck);
         const bool cubin_ready = have != g_cubins.end() && !have->second.empty();
         if (!e.fn && !e.failed && (jit_mode >= 2 || cubin_ready || e.work_seen >= 2e10)) {
@@ -304,7 +320,6 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
     }
     if (!fn) return cudaSuccess;
     if (tiles <= 0) { *launched = true; return cudaSuccess; }
-    void* params[] = {const_cast<LambdaArgs*>(&a), &out64, &out32, &steps};
     const CUresult r = driver().launch_kernel(fn, grid, 1, 1, (unsigned)threads, 1, 1, (unsigned)smem_bytes, (CUstream)st, params, nullptr);
     if (r != CUDA_SUCCESS) {
         std::lock_guard<std::mutex> lk(g_mu);
