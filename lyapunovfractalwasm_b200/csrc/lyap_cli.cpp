@@ -35,13 +35,14 @@ struct Options {
     int gpus = 1, frame = 0, frames = 0, repeat = 1;
     bool glow = false;
     bool gather = false;
+    bool quiet = false;   // no progress callback: the frame's lambda stage is then one kernel launch
 };
 
 [[noreturn]] void usage(const char* why) {
     std::cerr << "lyap_cli: " << why << "\n"
               << "usage: lyap_cli [--config 1..5 [--frame K] [--frames N [--repeat R]]] [--width W --height H --min-x .. --max-x .. --min-y .. --max-y ..]\n"
               << "                [--sequence S] [--iterations N] [--warmup N] [--c V] [--palette NAME]\n"
-              << "                [--mode exact|fast64|fast32] [--gpus N [--gather] [--repeat R]] [--glow] [--out file.ppm|.rgba|.f64]\n";
+              << "                [--mode exact|fast64|fast32] [--gpus N [--gather]] [--repeat R] [--quiet] [--glow] [--out file.ppm|.rgba|.f64]\n";
     std::exit(2);
 }
 
@@ -192,6 +193,7 @@ int main(int argc, char** argv) {
         else if (a == "--out") o.out = std::string(next());
         else if (a == "--glow") o.glow = true;
         else if (a == "--gather") o.gather = true;
+        else if (a == "--quiet") o.quiet = true;
         else usage("unknown option");
     }
 
@@ -221,9 +223,10 @@ int main(int argc, char** argv) {
     if (o.gpus <= 1) {
         lyap_ctx* ctx = nullptr;
         if ((status = lyap_create(&ctx, 0)) == LYAP_OK) {
-            status = lyap_render(ctx, &p, nullptr, nullptr, want_f64 ? norm.data() : nullptr, rgba.data(),
-                                 [](double f) { std::fprintf(stderr, "\rprogress %5.1f %%", 100.0 * f); }, &st);
-            std::fprintf(stderr, "\n");
+            for (int pass = 0; pass < std::max(1, o.repeat) && status == LYAP_OK; ++pass)
+                status = lyap_render(ctx, &p, nullptr, nullptr, want_f64 ? norm.data() : nullptr, rgba.data(),
+                                     o.quiet ? nullptr : +[](double f) { std::fprintf(stderr, "\rprogress %5.1f %%", 100.0 * f); }, &st);
+            if (!o.quiet) std::fprintf(stderr, "\n");
             lyap_destroy(ctx);
         }
     } else {

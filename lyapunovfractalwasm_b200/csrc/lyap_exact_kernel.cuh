@@ -42,7 +42,7 @@ constexpr size_t kTabSmemBytes = (size_t)LYAP_LOG_BINS * kTabCopies * sizeof(lya
 constexpr int kExpEntries = 4096;
 constexpr size_t kExpSmemBytes = (size_t)kExpEntries * sizeof(double2);                              // 64 KB
 constexpr size_t kExactSmemBytes = kTabSmemBytes + kExpSmemBytes;
-// after the tables: one tile of results (THREADS * P doubles) staged for 16-byte-per-lane stores
+// after the tables: one staging row per warp (32 * P doubles each) for 16-byte-per-lane stores of the results
 __host__ __device__ constexpr size_t exact_smem_bytes(int threads, int pixels_per_thread) {
     return kExactSmemBytes + (size_t)threads * pixels_per_thread * sizeof(double);
 }
@@ -497,22 +497,23 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
             if (!done[p]) lam[p] = valid[p] > 0 ? __ddiv_rn(lyap[p], __dmul_rn((double)valid[p], LYAP_LN2)) : -5.0;
         }
 
-        // stores: the tile's THREADS*P consecutive values go through a staging row in shared memory so that every lane
-        // writes 16 bytes and a warp's store covers 512 consecutive bytes, whatever P is; a ragged last tile or an
-        // output pointer that is not 16-byte aligned takes plain stores
+        // stores: each warp's 32*P consecutive values go through the warp's own staging row in shared memory, so that every
+        // lane writes 16 bytes and a store instruction covers consecutive 512-byte runs whatever P is (no block-wide barrier:
+        // warps stay out of step with each other); a ragged last tile or a misaligned output pointer takes plain stores
         const long long tile0 = tile * tile_px;
         const bool full_tile = tile0 + tile_px <= a.n_pixels;
-        double* stage = reinterpret_cast<double*>(smem_raw + kExactSmemBytes);
+        const int lane = threadIdx.x & 31, warp_px0 = (threadIdx.x & ~31) * P;
+        double* stage = reinterpret_cast<double*>(smem_raw + kExactSmemBytes) + warp_px0;
         if (out64) {
             if (full_tile && ((reinterpret_cast<uintptr_t>(out64 + tile0) & 15) == 0)) {
-                __syncthreads();   // the staging row is free (previous tile's readers are done)
+                __syncwarp();   // the row is free (this warp's reads of the previous tile are done)
 #pragma unroll
-                for (int p = 0; p < P; ++p) stage[threadIdx.x * P + p] = lam[p];
-                __syncthreads();
-                double2* dst = reinterpret_cast<double2*>(out64 + tile0);
+                for (int p = 0; p < P; ++p) stage[lane * P + p] = lam[p];
+                __syncwarp();
+                double2* dst = reinterpret_cast<double2*>(out64 + tile0 + warp_px0);
                 const double2* src = reinterpret_cast<const double2*>(stage);
 #pragma unroll
-                for (int i = threadIdx.x; i < THREADS * P / 2; i += THREADS) dst[i] = src[i];
+                for (int i = lane; i < 16 * P; i += 32) dst[i] = src[i];
             } else {
 #pragma unroll
                 for (int p = 0; p < P; ++p)
@@ -522,14 +523,14 @@ __device__ __forceinline__ void lambda_exact_body(const LambdaArgs& a, double* _
         if (out32) {
             if (full_tile && ((reinterpret_cast<uintptr_t>(out32 + tile0) & 15) == 0)) {
                 float* stage32 = reinterpret_cast<float*>(stage);
-                __syncthreads();
+                __syncwarp();
 #pragma unroll
-                for (int p = 0; p < P; ++p) stage32[threadIdx.x * P + p] = (float)lam[p];
-                __syncthreads();
-                float4* dst = reinterpret_cast<float4*>(out32 + tile0);
+                for (int p = 0; p < P; ++p) stage32[lane * P + p] = (float)lam[p];
+                __syncwarp();
+                float4* dst = reinterpret_cast<float4*>(out32 + tile0 + warp_px0);
                 const float4* src = reinterpret_cast<const float4*>(stage32);
 #pragma unroll
-                for (int i = threadIdx.x; i < THREADS * P / 4; i += THREADS) dst[i] = src[i];
+                for (int i = lane; i < 8 * P; i += 32) dst[i] = src[i];
             } else {
 #pragma unroll
                 for (int p = 0; p < P; ++p)

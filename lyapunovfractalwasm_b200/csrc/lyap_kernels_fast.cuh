@@ -5,7 +5,7 @@
 // arithmetic is rearranged for speed and is NOT bit-compatible with the reference:
 //   t = r*x;  deriv = fma(-2,t,r) = r(1-2x);  x' = fma(-t,x,t) = r x (1-x)         (4 fused ops/step)
 // and instead of one log per step the |deriv| are multiplied together; the product's exponent is
-// moved into an integer every 16 (fp64) or 12 (fp32) steps, and one log of the remaining mantissa is
+// moved into an integer at least every 32 (fp64) or 20 (fp32) steps, and one log of the remaining mantissa is
 // taken per pixel at the end:  sum log|deriv| = E*ln2 + log(mantissa product).
 // A chunk in which the orbit left (0,1) or a derivative was exactly zero is rolled back and redone
 // step by step with the reference's rules (skip zero terms, stop at the exit, keep the partial sum).
@@ -18,7 +18,7 @@ struct FastTraits;
 
 template <>
 struct FastTraits<double> {
-    static constexpr int kRenorm = 16;
+    static constexpr int kRenorm = 32;
     static __device__ __forceinline__ double fma_(double a, double b, double c) { return __fma_rn(a, b, c); }
     static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
     static __device__ __forceinline__ double abs_(double a) { return fabs(a); }
@@ -35,9 +35,10 @@ struct FastTraits<double> {
 template <>
 struct FastTraits<float> {
     // A product that is subnormal or zero when it is stripped sends the chunk to the step-by-step path.  Falling below
-    // 2^-126 from [1,2) takes five or more consecutive derivatives near 2^-25 (x within a few ulps of 0.5 each time);
-    // only a product that did so and was multiplied back above 2^-126 before the strip would lose low bits unnoticed.
-    static constexpr int kRenorm = 12;
+    // 2^-126 from [1,2) within 20 steps takes derivatives that average below 2^-6 (x within a percent of 0.5 step after
+    // step); only a product that did so and was multiplied back above 2^-126 before the strip would lose low bits
+    // unnoticed.  Where the strips fall does not change a regular pixel's bits (moving the exponent out is exact).
+    static constexpr int kRenorm = 20;
     static __device__ __forceinline__ float fma_(float a, float b, float c) { return __fmaf_rn(a, b, c); }
     static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
     static __device__ __forceinline__ float abs_(float a) { return fabsf(a); }
@@ -118,24 +119,35 @@ __device__ __noinline__ bool fast_careful_steps(FastPixel<T>* ps, T rA, T rB, T 
     return dead;
 }
 
-// Moves the exponent of every pixel's running product into its integer sum and notes the extreme exponent fields.
+// Moves the exponent of every pixel's running product into its integer sum and notes the smallest exponent field seen.
+// The sum takes the BIASED field; the caller subtracts the bias once per strip when it accepts the chunk.  Only the
+// low end needs watching: while x stays inside (0,1) every derivative is below r in magnitude, so a product of at most
+// kRenorm of them cannot overflow, and an x that left (0,1) is found by the test on x itself.
 template <typename T, int P>
-__device__ __forceinline__ void strip_products(T (&prod)[P], int (&esum)[P], int (&emin)[P], int (&emax)[P]) {
+__device__ __forceinline__ void strip_products(T (&prod)[P], int (&esum)[P], int (&emin)[P]) {
     using F = FastTraits<T>;
 #pragma unroll
     for (int p = 0; p < P; ++p) {
         const int e = F::strip(prod[p]);
         emin[p] = min(emin[p], e);
-        emax[p] = max(emax[p], e);
-        esum[p] += e - F::kBias;
+        esum[p] += e;
     }
+}
+
+// strips fast_fixed_groups makes in NG groups
+template <typename T>
+__host__ __device__ constexpr int strips_in_groups(int ng) {
+    int n = 0;
+    for (int gi = 0; gi < ng; ++gi)
+        if ((2 * (gi + 1)) % FastTraits<T>::kRenorm == 0 || gi == ng - 1) ++n;
+    return n;
 }
 
 // Run-time specialisation (see lyap_jit.cu): NG two-step groups whose patterns are compile-time constants
 // (PATS: 4 bits per group, repeating every KG groups), as one straight-line block; the products are stripped
 // every kRenorm steps and after the last group.
 template <typename T, int P, bool ACC, int KG, unsigned long long PATS, int NG, int GI = 0>
-__device__ __forceinline__ void fast_fixed_groups(T (&x)[P], T (&prod)[P], int (&esum)[P], int (&emin)[P], int (&emax)[P],
+__device__ __forceinline__ void fast_fixed_groups(T (&x)[P], T (&prod)[P], int (&esum)[P], int (&emin)[P],
                                                   const T (&rA)[P], const T (&rB)[P], const T (&rC)[P]) {
     using F = FastTraits<T>;
     if constexpr (GI < NG) {
@@ -152,8 +164,8 @@ __device__ __forceinline__ void fast_fixed_groups(T (&x)[P], T (&prod)[P], int (
                 x[p] = F::fma_(-t, x[p], t);
             }
         }
-        if (ACC && ((2 * (GI + 1)) % F::kRenorm == 0 || GI == NG - 1)) strip_products<T, P>(prod, esum, emin, emax);
-        fast_fixed_groups<T, P, ACC, KG, PATS, NG, GI + 1>(x, prod, esum, emin, emax, rA, rB, rC);
+        if (ACC && ((2 * (GI + 1)) % F::kRenorm == 0 || GI == NG - 1)) strip_products<T, P>(prod, esum, emin);
+        fast_fixed_groups<T, P, ACC, KG, PATS, NG, GI + 1>(x, prod, esum, emin, rA, rB, rC);
     }
 }
 
@@ -218,7 +230,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
             if constexpr (KG > 0) {
                 // exit tests after REP straight-line blocks of CB whole periods (measured: 1 -> 4 blocks saves 12 % (fp64) and
                 // 16 % (fp32) of a large frame's time, 8 another 2 %; a pixel that leaves (0,1) replays at most one such chunk)
-                constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, REP = 4, CS = CB * BS * REP;
+                constexpr int BS = 2 * KG, CB = (kStepsPerWord + BS - 1) / BS, REP = 8, CS = CB * BS * REP;
                 const unsigned* sel = a.sel + word0;
                 int s = 0;
                 while (s < nsteps) {
@@ -229,30 +241,33 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                     const int left = nsteps - s;
                     const int n = left >= CS ? CS : (left >= CB * BS ? CB * BS : (left >= BS ? left / BS * BS : left));
                     T sx[P], sp[P];
-                    int se[P], emin[P], emax[P];
+                    int se[P], emin[P];
+                    int nstrip = 0;   // strips made in this chunk (the same for every pixel): their bias leaves the sums below
 #pragma unroll
                     for (int p = 0; p < P; ++p) {
                         sx[p] = x[p];
                         sp[p] = prod[p];
                         se[p] = esum[p];
                         emin[p] = F::kExpMax;
-                        emax[p] = 0;
                     }
                     if (left >= CS) {
 #pragma unroll 1
                         for (int rep = 0; rep < REP; ++rep) {
-                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
-                            else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
+                            else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         }
+                        nstrip = REP * strips_in_groups<T>(CB * KG);
                     } else if (left >= CB * BS) {
-                        if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
-                        else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                        if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
+                        else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
+                        nstrip = strips_in_groups<T>(CB * KG);
                     } else if (left >= BS) {
 #pragma unroll 1
                         for (int b = 0; b < n / BS; ++b) {
-                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, KG>(x, prod, esum, emin, emax, rA, rB, rC);
-                            else fast_fixed_groups<T, P, false, KG, WU_PATS, KG>(x, prod, esum, emin, emax, rA, rB, rC);
+                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
+                            else fast_fixed_groups<T, P, false, KG, WU_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
                         }
+                        nstrip = (n / BS) * strips_in_groups<T>(KG);
                     } else {
 #pragma unroll 1
                         for (int j = s; j < nsteps; ++j) {
@@ -261,7 +276,10 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                                 if (code == 0) fast_mode_steps<T, P, true>(x, prod, rA);
                                 else if (code == 1) fast_mode_steps<T, P, true>(x, prod, rB);
                                 else fast_mode_steps<T, P, true>(x, prod, rC);
-                                if ((j - s + 1) % F::kRenorm == 0 || j == nsteps - 1) strip_products<T, P>(prod, esum, emin, emax);
+                                if ((j - s + 1) % F::kRenorm == 0 || j == nsteps - 1) {
+                                    strip_products<T, P>(prod, esum, emin);
+                                    ++nstrip;
+                                }
                             } else {
                                 if (code == 0) fast_mode_steps<T, P, false>(x, prod, rA);
                                 else if (code == 1) fast_mode_steps<T, P, false>(x, prod, rB);
@@ -272,10 +290,12 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
 #pragma unroll
                     for (int p = 0; p < P; ++p) {
                         if (done[p]) continue;
-                        const bool regular = !careful_only[p] && (x[p] > (T)0 && x[p] < (T)1) &&
-                                             (!acc || (emin[p] != 0 && emax[p] != F::kExpMax));
+                        const bool regular = !careful_only[p] && (x[p] > (T)0 && x[p] < (T)1) && (!acc || emin[p] != 0);
                         if (regular) {
-                            if (acc) valid[p] += n;
+                            if (acc) {
+                                valid[p] += n;
+                                esum[p] -= F::kBias * nstrip;
+                            }
                             my_steps += (unsigned long long)n;
                         } else {
                             esum[p] = se[p];
@@ -309,18 +329,18 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                 if (++wi == wrap) wi = 0;
                 const int n = min(kStepsPerWord, nsteps - c * kStepsPerWord);
                 T sx[P], sp[P];
-                int se[P], emin[P], emax[P];
+                int se[P], emin[P];
+                int nstrip = 0;
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     sx[p] = x[p];
                     sp[p] = prod[p];
                     se[p] = esum[p];
                     emin[p] = F::kExpMax;
-                    emax[p] = 0;
                 }
                 unsigned w = word;
                 if (acc) {
-                    for (int j0 = 0; j0 < n; j0 += F::kRenorm) {
+                    for (int j0 = 0; j0 < n; j0 += F::kRenorm, ++nstrip) {
                         const int jn = min(F::kRenorm, n - j0);
                         for (int j = 0; j < jn; ++j, w >>= 2) {
                             const unsigned sel = w & 3u;
@@ -328,13 +348,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             else if (sel == 1) fast_mode_steps<T, P, true>(x, prod, rB);
                             else fast_mode_steps<T, P, true>(x, prod, rC);
                         }
-#pragma unroll
-                        for (int p = 0; p < P; ++p) {
-                            const int e = F::strip(prod[p]);
-                            emin[p] = min(emin[p], e);
-                            emax[p] = max(emax[p], e);
-                            esum[p] += e - F::kBias;
-                        }
+                        strip_products<T, P>(prod, esum, emin);
                     }
                 } else {
                     for (int j = 0; j < n; ++j, w >>= 2) {
@@ -347,11 +361,13 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     if (done[p]) continue;
-                    // a zero derivative or an overflow shows as exponent field 0 / all ones
-                    const bool regular = !careful_only[p] && (x[p] > (T)0 && x[p] < (T)1) &&
-                                         (!acc || (emin[p] != 0 && emax[p] != F::kExpMax));
+                    // a zero derivative (or a product that underflowed) shows as exponent field 0
+                    const bool regular = !careful_only[p] && (x[p] > (T)0 && x[p] < (T)1) && (!acc || emin[p] != 0);
                     if (regular) {
-                        if (acc) valid[p] += n;
+                        if (acc) {
+                            valid[p] += n;
+                            esum[p] -= F::kBias * nstrip;
+                        }
                         my_steps += (unsigned long long)n;
                     } else {
                         esum[p] = se[p];
@@ -377,21 +393,23 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
 #pragma unroll
         for (int p = 0; p < P; ++p)
             if (!done[p]) lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
-        // stores through a staging row in shared memory: 16 bytes per lane, 512 consecutive bytes per warp
-        // (plain stores for a ragged last tile or an output pointer that is not 16-byte aligned)
+        // stores through the warp's own staging row in shared memory: 16 bytes per lane, consecutive 512-byte runs per
+        // instruction, no block-wide barrier (plain stores for a ragged last tile or a misaligned output pointer)
         const long long tile0 = tile * tile_px;
         const bool full_tile = tile0 + tile_px <= a.n_pixels;
-        __shared__ __align__(16) double stage[THREADS * P];
+        __shared__ __align__(16) double stage_all[THREADS * P];
+        const int lane = threadIdx.x & 31, warp_px0 = (threadIdx.x & ~31) * P;
+        double* stage = stage_all + warp_px0;
         if (out64) {
             if (full_tile && ((reinterpret_cast<uintptr_t>(out64 + tile0) & 15) == 0)) {
-                __syncthreads();
+                __syncwarp();
 #pragma unroll
-                for (int p = 0; p < P; ++p) stage[threadIdx.x * P + p] = lam[p];
-                __syncthreads();
-                double2* dst = reinterpret_cast<double2*>(out64 + tile0);
+                for (int p = 0; p < P; ++p) stage[lane * P + p] = lam[p];
+                __syncwarp();
+                double2* dst = reinterpret_cast<double2*>(out64 + tile0 + warp_px0);
                 const double2* src = reinterpret_cast<const double2*>(stage);
 #pragma unroll
-                for (int i = threadIdx.x; i < THREADS * P / 2; i += THREADS) dst[i] = src[i];
+                for (int i = lane; i < 16 * P; i += 32) dst[i] = src[i];
             } else {
 #pragma unroll
                 for (int p = 0; p < P; ++p)
@@ -401,14 +419,14 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
         if (out32) {
             if (full_tile && ((reinterpret_cast<uintptr_t>(out32 + tile0) & 15) == 0)) {
                 float* stage32 = reinterpret_cast<float*>(stage);
-                __syncthreads();
+                __syncwarp();
 #pragma unroll
-                for (int p = 0; p < P; ++p) stage32[threadIdx.x * P + p] = (float)lam[p];
-                __syncthreads();
-                float4* dst = reinterpret_cast<float4*>(out32 + tile0);
+                for (int p = 0; p < P; ++p) stage32[lane * P + p] = (float)lam[p];
+                __syncwarp();
+                float4* dst = reinterpret_cast<float4*>(out32 + tile0 + warp_px0);
                 const float4* src = reinterpret_cast<const float4*>(stage32);
 #pragma unroll
-                for (int i = threadIdx.x; i < THREADS * P / 4; i += THREADS) dst[i] = src[i];
+                for (int i = lane; i < 8 * P; i += 32) dst[i] = src[i];
             } else {
 #pragma unroll
                 for (int p = 0; p < P; ++p)
