@@ -19,6 +19,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <tuple>
 #include <vector>
 
@@ -51,8 +52,10 @@ struct Driver {
     bool ok = false;
 };
 
-std::mutex g_mu;
-std::string g_note;   // last reason a specialised kernel could not be used
+// Process-wide state lives in objects that are never destroyed: a background compilation may still be running when the
+// process leaves main, and must not find them gone.
+std::mutex& g_mu = *new std::mutex;
+std::string& g_note = *new std::string;   // last reason a specialised kernel could not be used
 
 Nvrtc& nvrtc() {
     static Nvrtc n = [] {
@@ -107,17 +110,19 @@ struct Entry {
     double work_seen = 0;   // nominal steps asked for so far with this key (decides when compiling pays off)
 };
 
-std::map<Key, Entry> g_cache;
+std::map<Key, Entry>& g_cache = *new std::map<Key, Entry>;
 // compiled code does not depend on the device ordinal: one compilation serves every GPU of the process
 using CodeKey = std::tuple<int, int, unsigned long long, unsigned long long, int, int, int>;   // Key without the device
-std::map<CodeKey, std::vector<char>> g_cubins;
+std::map<CodeKey, std::vector<char>>& g_cubins = *new std::map<CodeKey, std::vector<char>>;
+// run-time compilations handed to a background thread: 1 = running, 2 = failed (a finished one is in g_cubins)
+std::map<CodeKey, int>& g_background = *new std::map<CodeKey, int>;
 
 // NVRTC: source text + pattern macros -> cubin for sm_100a.
-bool compile_cubin(const Key& key, std::vector<char>* out) {
+bool compile_cubin(const Key& key, std::vector<char>* out, std::string* note) {
     Nvrtc& n = nvrtc();
     const int kind = std::get<5>(key);
     std::vector<char>& cubin = *out;
-    if (!n.ok) { g_note = "NVRTC library not found"; return false; }
+    if (!n.ok) { *note = "NVRTC library not found"; return false; }
     char o_p[64], o_kg[64], o_wu[96], o_acc[96], o_thr[64];
     snprintf(o_thr, sizeof o_thr, "-DLYAP_SPEC_THREADS=%d", std::get<6>(key));
     // the exact instance is compiled when LYAP_SPEC_KG is defined without a fast type; a fast one when the type is given
@@ -135,7 +140,7 @@ bool compile_cubin(const Key& key, std::vector<char>* out) {
     static const char kMain[] = "#include \"lyap_exact_kernel.cuh\"\n#include \"lyap_kernels_fast.cuh\"\n";
     nvrtcProgram prog = nullptr;
     if (n.create(&prog, kMain, "lyap_spec.cu", 5, header_src, header_names) != NVRTC_SUCCESS) {
-        g_note = "nvrtcCreateProgram failed";
+        *note = "nvrtcCreateProgram failed";
         return false;
     }
     const nvrtcResult rc = n.compile(prog, (int)(sizeof(opts) / sizeof(opts[0])), opts);
@@ -144,13 +149,13 @@ bool compile_cubin(const Key& key, std::vector<char>* out) {
         n.log_size(prog, &ls);
         std::string log(ls, '\0');
         if (ls) n.log(prog, log.data());
-        g_note = "run-time compilation failed: " + log.substr(0, 600);
+        *note = "run-time compilation failed: " + log.substr(0, 600);
         n.destroy(&prog);
         return false;
     }
     size_t cs = 0;
     if (n.cubin_size(prog, &cs) != NVRTC_SUCCESS || cs == 0) {
-        g_note = "no cubin produced";
+        *note = "no cubin produced";
         n.destroy(&prog);
         return false;
     }
@@ -169,7 +174,7 @@ bool compile_entry(const Key& key, Entry* e, size_t smem_bytes, const PrebuiltKe
     std::vector<char>& cubin = g_cubins[ck];
     if (cubin.empty() && embedded) cubin.assign(reinterpret_cast<const char*>(embedded->cubin),
                                                 reinterpret_cast<const char*>(embedded->cubin) + embedded->cubin_bytes);
-    if (cubin.empty() && !compile_cubin(key, &cubin)) {
+    if (cubin.empty() && !compile_cubin(key, &cubin, &g_note)) {
         cubin.clear();
         return false;
     }
@@ -313,8 +318,32 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
         const CodeKey ck{pixels_per_thread, kg, wu, acc, kind, threads, 0};
         const auto have = g_cubins.find(ck);
         const bool cubin_ready = have != g_cubins.end() && !have->second.empty();
-        if (!e.fn && !e.failed && (jit_mode >= 2 || cubin_ready || e.work_seen >= 2e10)) {
-            if (!compile_entry(key, &e, smem_bytes)) e.failed = true;
+        if (!e.fn && !e.failed) {
+            if (jit_mode >= 2 || cubin_ready) {
+                if (!compile_entry(key, &e, smem_bytes)) e.failed = true;   // compiles if need be, loads into this device's context
+            } else if (e.work_seen >= 2e10) {
+                // Compile on a background thread; launches go on with the generic kernel and switch over once the code
+                // is there (loading it is quick and is done above, by whichever launch comes next).
+                int& state = g_background[ck];
+                if (state == 2) {
+                    e.failed = true;
+                } else if (state == 0) {
+                    state = 1;
+                    std::thread([key, ck]() {
+                        std::vector<char> cubin;
+                        std::string note;
+                        const bool ok = compile_cubin(key, &cubin, &note);
+                        std::lock_guard<std::mutex> lk2(g_mu);
+                        if (ok) {
+                            g_cubins[ck] = std::move(cubin);
+                            g_background[ck] = 0;
+                        } else {
+                            g_note = note;
+                            g_background[ck] = 2;
+                        }
+                    }).detach();
+                }
+            }
         }
         fn = e.fn;
     }

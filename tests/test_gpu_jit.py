@@ -148,3 +148,40 @@ def test_runs_longer_than_the_selector_table(engine, port, kernel_path, case):
             w = want[:-1, :-1]
             assert np.array_equal(f == -5.0, w == -5.0)
             assert np.median(np.abs(f - w)) < tol, (mode, fast)
+
+
+def test_default_mode_compiles_in_the_background(engine, port):
+    """The default (LYAP_JIT=1): once about 2e10 steps of work with a sequence have been asked for, an instance is
+    compiled on a background thread; launches meanwhile use the generic kernel (no stall), later ones the new instance,
+    and the bits are the same before and after."""
+    import os
+    import time
+    old = {k: os.environ.get(k) for k in ("LYAP_JIT", "LYAP_PREBUILT")}
+    os.environ["LYAP_JIT"], os.environ["LYAP_PREBUILT"] = "1", "0"
+    try:
+        kw = dict(min_x=2.6, max_x=3.95, min_y=2.7, max_y=3.9, width=1024, height=1024, sequence="ABAAB", iterations=9000,
+                  warmup=1000)                                          # 1.05e10 steps a frame
+        small = dict(kw, width=96, height=8)
+        want, _ = oracle(port, small)
+        first = engine.render(L.make_params(**kw), want=("lambda",))["lambda"]
+        assert "generic" in engine.lib.lyap_last_kernel().decode()       # below the threshold
+        t0 = time.time()
+        second = engine.render(L.make_params(**kw), want=("lambda",))["lambda"]     # crosses it: compilation starts, no wait
+        assert time.time() - t0 < 0.5 and "generic" in engine.lib.lyap_last_kernel().decode()
+        name = ""
+        while time.time() - t0 < 60 and "compiled at run time" not in name:
+            time.sleep(0.2)
+            r = engine.render(L.make_params(**small), want=("lambda",))
+            assert np.array_equal(r["lambda"].view(np.uint64), want.view(np.uint64))
+            # the small frame takes another shape (2 pixels per thread): keep asking with the large one's shape too
+            third = engine.render(L.make_params(**kw), want=("lambda",))["lambda"]
+            name = engine.lib.lyap_last_kernel().decode()
+        assert "compiled at run time" in name, (name, engine.lib.lyap_jit_note())
+        assert np.array_equal(first.view(np.uint64), second.view(np.uint64))
+        assert np.array_equal(first.view(np.uint64), third.view(np.uint64))
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
