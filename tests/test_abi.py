@@ -50,6 +50,7 @@ def test_struct_layout_matches_header():
     assert ctypes.sizeof(L.LyapParams) == 104
     assert L.LyapParams.sequence.offset == 40 and L.LyapParams.c_value.offset == 80
     assert ctypes.sizeof(L.RenderStats) == 64
+    assert ctypes.sizeof(L.MultiStats) == 64 and L.MultiStats.gather_bytes.offset == 48
 
 
 def test_drop_in_header_compiles_as_cxx23(tmp_path):
@@ -86,6 +87,9 @@ def test_fails_loudly_without_a_device():
     frames = [L.make_params(width=8, height=8, sequence="AB", iterations=10, warmup=2) for _ in range(3)]
     with pytest.raises(L.LyapError) as ei:          # the batch entry point: same rule, reported from its worker thread
         L.render_frames(frames, [0])
+    assert ei.value.status == 4
+    with pytest.raises(L.LyapError) as ei:          # the kept multi-device object: same rule
+        L.Multi([0], use_nccl=True)
     assert ei.value.status == 4
     with pytest.raises(L.LyapError) as ei:          # argument errors come before any device is touched
         L.render_frames([L.make_params(width=8, height=8, sequence="", iterations=10, warmup=2)], [0])
