@@ -12,8 +12,8 @@ each rank renders one 4096-row band (weak scaling); the only exchange is one all
 
 Beside that headline the JSON line carries (unless --no-extras):
   strong_cfg4   the one 65536x65536 "AB" frame split into N row bands (strong scaling; N = 1 holds 80 GiB)
-  modes         (N = 1) the fast fp64 / fast fp32 kernels on the 4096x4096 frame: ms per frame, pipe fraction,
-                per-pixel deviation from the exact frame
+  modes         (N = 1) the fast kernels (fused fp64, fused fp32, fp64 on the exact orbit) on the 4096x4096 frame: ms per
+                frame, pipe fraction, per-pixel deviation from the exact frame
   c_abi_multi   rank 0 alone drives all N devices from one process through the C ABI's lyap_multi object:
                 the 16384x16384 frame as N bands with the NCCL gather of the RGBA bands into device 0, and a
                 batch of zoom frames dealt round-robin (the other ranks wait on the host meanwhile)
@@ -136,7 +136,15 @@ class CpuReference:
         self.ref = O.ref("stock")
         self.port = O.port()
         self.kind = "reference" if self.ref is not None else "port"
-        self.threads = self.ref.max_threads() if self.ref is not None else (os.cpu_count() or 1)
+        # all the host CPUs this process may run on, whatever OMP_NUM_THREADS says (torch.distributed.run sets it to 1 for
+        # every worker it starts); what the header's loop will really use is read back from the OpenMP runtime
+        cpus = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        if self.ref is not None:
+            self.ref.set_threads(cpus)
+            self.threads = self.ref.max_threads()
+        else:
+            os.environ["OMP_NUM_THREADS"] = str(cpus)
+            self.threads = cpus
         self.w = CFG2["width"]
         self.per_px = CFG2["warmup"] + CFG2["iterations"]
 
@@ -237,7 +245,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--mode", default="exact", choices=["exact", "fast64", "fast32"])
+    ap.add_argument("--mode", default="exact", choices=["exact", "fast64", "fast32", "orbit64"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="2 (default): the 4096-wide frame, one 4096-row band per GPU; 3, 4: that frame split over the GPUs")
@@ -273,7 +281,7 @@ def main():
     stream = torch.cuda.Stream()          # a real stream handle: the engine, the events and NCCL's waits all use it
     torch.cuda.set_stream(stream)
     eng.set_stream(ctypes.c_void_p(stream.cuda_stream))
-    modes = {"exact": L.MODE_EXACT, "fast64": L.MODE_FAST_FP64, "fast32": L.MODE_FAST_FP32}
+    modes = {"exact": L.MODE_EXACT, "fast64": L.MODE_FAST_FP64, "fast32": L.MODE_FAST_FP32, "orbit64": L.MODE_FAST_FP64_ORBIT}
     mode = modes[args.mode]
     dev = torch.device("cuda", local_rank)
 
@@ -366,6 +374,9 @@ def main():
             if md == L.MODE_EXACT:
                 ops = OPS_WARM * kw["warmup"] + OPS_ACC * kw["iterations"]
                 flops = FLOPS_WARM * kw["warmup"] + FLOPS_ACC * kw["iterations"]
+            elif md == L.MODE_FAST_FP64_ORBIT:      # the reference's 3 orbit operations; fma(-2,x,1), r*|.| and the product when accumulating
+                ops = 3 * kw["warmup"] + 6 * kw["iterations"]
+                flops = 3 * kw["warmup"] + 7 * kw["iterations"]
             else:
                 ops, flops = FAST_OPS * per_px_steps, FAST_FLOPS * per_px_steps
             steps_per_launch = m["executed"] / m["steps"] / world * self.rows_all / self.rows_own   # one rank's launch, halo included
@@ -502,7 +513,7 @@ def main():
             stable = (exact < 0) & (exact > -4)
             chaotic = exact >= 0
             out = {}
-            for name, md in (("fast64", L.MODE_FAST_FP64), ("fast32", L.MODE_FAST_FP32)):
+            for name, md in (("fast64", L.MODE_FAST_FP64), ("fast32", L.MODE_FAST_FP32), ("orbit64", L.MODE_FAST_FP64_ORBIT)):
                 fr = BandRunner(dict(kw, mode=md))
                 fm = fr.measure(5, 3)
                 fp = fr.pipe_numbers(fm, fp64_peak, fp32_peak)

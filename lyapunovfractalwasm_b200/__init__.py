@@ -13,7 +13,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblyap_b200.so")
 
-MODE_EXACT, MODE_FAST_FP64, MODE_FAST_FP32 = 0, 1, 2
+MODE_EXACT, MODE_FAST_FP64, MODE_FAST_FP32, MODE_FAST_FP64_ORBIT = 0, 1, 2, 3
 PALETTES = ["cosmic", "nebula", "aurora", "solarflare", "blackhole", "psychedelic", "rainbow"]
 
 c_double_p = ctypes.POINTER(ctypes.c_double)

@@ -98,7 +98,7 @@ int build_args(const lyap_params* p, lyap::LambdaArgs* a, Geometry* g) {
     if (!p) return fail(LYAP_ERR_INVALID, "params is null");
     if (p->width < 1 || p->height < 1) return fail(LYAP_ERR_INVALID, "width and height must be >= 1");
     if (p->iterations < 0 || p->warmup < 0) return fail(LYAP_ERR_INVALID, "iterations and warmup must be >= 0");
-    if (p->mode < LYAP_MODE_EXACT || p->mode > LYAP_MODE_FAST_FP32) return fail(LYAP_ERR_INVALID, "unknown mode");
+    if (p->mode < LYAP_MODE_EXACT || p->mode > LYAP_MODE_FAST_FP64_ORBIT) return fail(LYAP_ERR_INVALID, "unknown mode");
     // the fast kernels keep each pixel's exponent sum in 32 bits: a derivative's exponent is at most 2 and, short of an
     // exact zero (handled apart), no less than about -60, so 2^24 steps stay far inside the range
     if (p->mode != LYAP_MODE_EXACT && (long long)p->iterations + p->warmup > (1LL << 24))
@@ -166,6 +166,7 @@ int launch_lambda(lyap_ctx* c, int mode, const lyap::LambdaArgs& a, double* d64,
     cudaError_t e;
     if (mode == LYAP_MODE_EXACT) e = lyap::launch_lambda_exact(a, d64, d32, steps, c->sm_count, c->stream);
     else if (mode == LYAP_MODE_FAST_FP64) e = lyap::launch_lambda_fast64(a, d64, d32, steps, c->sm_count, c->stream);
+    else if (mode == LYAP_MODE_FAST_FP64_ORBIT) e = lyap::launch_lambda_orbit64(a, d64, d32, steps, c->sm_count, c->stream);
     else e = lyap::launch_lambda_fast32(a, d64, d32, steps, c->sm_count, c->stream);
     if (e != cudaSuccess) return fail_cuda(e, "lambda kernel launch");
     return LYAP_OK;

@@ -42,7 +42,7 @@ struct Options {
     std::cerr << "lyap_cli: " << why << "\n"
               << "usage: lyap_cli [--config 1..5 [--frame K] [--frames N [--repeat R]]] [--width W --height H --min-x .. --max-x .. --min-y .. --max-y ..]\n"
               << "                [--sequence S] [--iterations N] [--warmup N] [--c V] [--palette NAME]\n"
-              << "                [--mode exact|fast64|fast32] [--gpus N [--gather]] [--repeat R] [--quiet] [--glow] [--out file.ppm|.rgba|.f64]\n";
+              << "                [--mode exact|fast64|fast32|orbit64] [--gpus N [--gather]] [--repeat R] [--quiet] [--glow] [--out file.ppm|.rgba|.f64]\n";
     std::exit(2);
 }
 
@@ -203,8 +203,9 @@ int main(int argc, char** argv) {
     p.width = o.width; p.height = o.height;
     p.sequence = o.sequence.data(); p.sequence_len = static_cast<int32_t>(o.sequence.size());
     p.iterations = o.iterations; p.warmup = o.warmup;
-    p.mode = o.mode == "exact" ? LYAP_MODE_EXACT : o.mode == "fast64" ? LYAP_MODE_FAST_FP64 : o.mode == "fast32" ? LYAP_MODE_FAST_FP32 : -1;
-    if (p.mode < 0) usage("--mode takes exact, fast64 or fast32");
+    p.mode = o.mode == "exact" ? LYAP_MODE_EXACT : o.mode == "fast64" ? LYAP_MODE_FAST_FP64 : o.mode == "fast32" ? LYAP_MODE_FAST_FP32
+             : o.mode == "orbit64" ? LYAP_MODE_FAST_FP64_ORBIT : -1;
+    if (p.mode < 0) usage("--mode takes exact, fast64, fast32 or orbit64");
     p.palette = lyap_palette_from_name(o.palette.c_str());
     p.c_enabled = o.has_c ? 1 : 0;
     p.c_value = o.c;

@@ -16,8 +16,10 @@ cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out3
                                  int sm_count, cudaStream_t st);
 cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                  int sm_count, cudaStream_t st);
+cudaError_t launch_lambda_orbit64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                  int sm_count, cudaStream_t st);
 
-// Instance of a lambda kernel made for the sequence's patterns (lyap_jit.cu); kind: 0 exact, 1 fast fp64, 2 fast fp32.
+// Instance of a lambda kernel made for the sequence's patterns (lyap_jit.cu); kind: 0 exact, 1 fast fp64, 2 fast fp32, 3 fast fp64 on the exact orbit.
 // *launched == false means "not used, launch the generic kernel".  mode: low two bits say when to compile at run time
 // (0 never, 1 once enough work with this sequence has been seen, 2 at once); kSpecUsePrebuilt allows the instances
 // compiled at build time (lyap_prebuilt.cu), which are tried first.
@@ -33,7 +35,7 @@ void note_lambda_kernel(const char* text);
 
 // A lambda kernel compiled at build time for one sequence's patterns: device code (a cubin for sm_100a) embedded in the
 // library, made by build.py with the same compiler, source text and options as a run-time instance (lyap_prebuilt.cu).
-// kind: 0 exact, 1 fast fp64, 2 fast fp32.  launch_lambda_spec prefers a matching entry to compiling at run time.
+// kind: 0 exact, 1 fast fp64, 2 fast fp32, 3 fast fp64 on the exact orbit.  launch_lambda_spec prefers a matching entry to compiling at run time.
 struct PrebuiltKernel {
     int kind, pixels_per_thread, threads, kg;
     unsigned long long wu_pats, acc_pats;

@@ -125,8 +125,10 @@ bool compile_cubin(const Key& key, std::vector<char>* out, std::string* note) {
     if (!n.ok) { *note = "NVRTC library not found"; return false; }
     char o_p[64], o_kg[64], o_wu[96], o_acc[96], o_thr[64];
     snprintf(o_thr, sizeof o_thr, "-DLYAP_SPEC_THREADS=%d", std::get<6>(key));
-    // the exact instance is compiled when LYAP_SPEC_KG is defined without a fast type; a fast one when the type is given
-    const char* o_kind = kind == 0 ? "-DLYAP_SPEC_EXACT=1" : (kind == 1 ? "-DLYAP_SPEC_FAST_TYPE=double" : "-DLYAP_SPEC_FAST_TYPE=float");
+    // the exact instance is compiled when LYAP_SPEC_EXACT is defined; a fast one when LYAP_SPEC_FAST names its flavour
+    static const char* const kind_opts[4] = {"-DLYAP_SPEC_EXACT=1", "-DLYAP_SPEC_FAST=FusedF64", "-DLYAP_SPEC_FAST=FusedF32",
+                                             "-DLYAP_SPEC_FAST=OrbitF64"};
+    const char* o_kind = kind_opts[kind];
     snprintf(o_p, sizeof o_p, "-DLYAP_SPEC_P=%d", std::get<1>(key));
     snprintf(o_kg, sizeof o_kg, "-DLYAP_SPEC_KG=%d", std::get<2>(key));
     snprintf(o_wu, sizeof o_wu, "-DLYAP_SPEC_WU_PATS=0x%llxull", std::get<3>(key));
@@ -263,7 +265,7 @@ cudaError_t launch_lambda_spec(const LambdaArgs& a, double* out64, float* out32,
     const long long cap = kind == 0 ? sm_count : 4LL * sm_count;   // the exact kernel's shared tables allow one CTA per SM
     const unsigned grid = (unsigned)(tiles < cap ? tiles : cap);
     char name[160];
-    static const char* const kinds[3] = {"k_lambda_exact", "k_lambda_fast<double>", "k_lambda_fast<float>"};
+    static const char* const kinds[4] = {"k_lambda_exact", "k_lambda_fast<FusedF64>", "k_lambda_fast<FusedF32>", "k_lambda_fast<OrbitF64>"};
 
     int dev = 0;
     cudaError_t ce = cudaGetDevice(&dev);

@@ -605,14 +605,12 @@ cudaError_t launch_fp32_peak(float* sink, int sm_count, int iters, unsigned long
 
 namespace lyap {
 
-template <typename T, int P>
+template <typename FL, int P>
 static cudaError_t launch_lambda_fast_t(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
-                                        int sm_count, cudaStream_t st) {
+                                        int sm_count, cudaStream_t st, int kind, int spec_ppt, const char* generic_name) {
     {   // a periodic sequence can run an instance made for its patterns (same switches as the exact kernel)
         bool launched = false;
-        // measured best shapes for the specialised instances: fp64 4 pixels/thread, fp32 2 pixels/thread, 512 threads
-        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, sizeof(T) == 8 ? 1 : 2,
-                                                 sizeof(T) == 8 ? 4 : 2, 512, 0, spec_mode(), &launched);
+        const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, kind, spec_ppt, 512, 0, spec_mode(), &launched);
         if (e != cudaSuccess) return e;
         if (launched) return cudaSuccess;
     }
@@ -620,25 +618,31 @@ static cudaError_t launch_lambda_fast_t(const LambdaArgs& a, double* out64, floa
     const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) return cudaSuccess;
     int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_lambda_fast<T, P, kFastThreads>,
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_lambda_fast<FL, P, kFastThreads>,
                                                                   kFastThreads, 0);
     if (e != cudaSuccess) return e;
     if (per_sm < 1) per_sm = 1;
     const long long cap = (long long)sm_count * per_sm;
     const int grid = (int)(tiles < cap ? tiles : cap);
-    k_lambda_fast<T, P, kFastThreads><<<grid, kFastThreads, 0, st>>>(a, out64, out32, steps);
-    note_lambda_kernel(sizeof(T) == 8 ? "k_lambda_fast<double,4,256> (generic)" : "k_lambda_fast<float,4,256> (generic)");
+    k_lambda_fast<FL, P, kFastThreads><<<grid, kFastThreads, 0, st>>>(a, out64, out32, steps);
+    note_lambda_kernel(generic_name);
     return cudaGetLastError();
 }
 
+// measured best shapes for the instances made for a sequence: fp64 4 pixels/thread, fp32 2 pixels/thread, 512 threads
 cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                  int sm_count, cudaStream_t st) {
-    return launch_lambda_fast_t<double, 4>(a, out64, out32, steps, sm_count, st);
+    return launch_lambda_fast_t<FusedF64, 4>(a, out64, out32, steps, sm_count, st, 1, 4, "k_lambda_fast<FusedF64,4,256> (generic)");
 }
 
 cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                  int sm_count, cudaStream_t st) {
-    return launch_lambda_fast_t<float, 4>(a, out64, out32, steps, sm_count, st);
+    return launch_lambda_fast_t<FusedF32, 4>(a, out64, out32, steps, sm_count, st, 2, 2, "k_lambda_fast<FusedF32,4,256> (generic)");
+}
+
+cudaError_t launch_lambda_orbit64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
+                                  int sm_count, cudaStream_t st) {
+    return launch_lambda_fast_t<OrbitF64, 4>(a, out64, out32, steps, sm_count, st, 3, 4, "k_lambda_fast<OrbitF64,4,256> (generic)");
 }
 
 }  // namespace lyap

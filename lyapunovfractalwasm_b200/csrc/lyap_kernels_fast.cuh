@@ -21,6 +21,7 @@ struct FastTraits<double> {
     static constexpr int kRenorm = 32;
     static __device__ __forceinline__ double fma_(double a, double b, double c) { return __fma_rn(a, b, c); }
     static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
+    static __device__ __forceinline__ double sub(double a, double b) { return __dsub_rn(a, b); }
     static __device__ __forceinline__ double abs_(double a) { return fabs(a); }
     // returns biased exponent; rewrites v's exponent to 0 (mantissa in [1,2)); sign assumed +
     static __device__ __forceinline__ int strip(double& v) {
@@ -41,6 +42,7 @@ struct FastTraits<float> {
     static constexpr int kRenorm = 20;
     static __device__ __forceinline__ float fma_(float a, float b, float c) { return __fmaf_rn(a, b, c); }
     static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+    static __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
     static __device__ __forceinline__ float abs_(float a) { return fabsf(a); }
     static __device__ __forceinline__ int strip(float& v) {
         const unsigned u = __float_as_uint(v);
@@ -51,6 +53,30 @@ struct FastTraits<float> {
     static constexpr int kExpMax = 255;
 };
 
+// The three fast kernels: which type the orbit and the product run in, and whether the orbit and the derivative use the
+// reference's own operations (then x and every derivative have the exact kernel's bits and only the accumulation --
+// a running product instead of a sum of logarithms -- differs) or the fused ones.
+struct FusedF64 { using real = double; static constexpr bool same_orbit = false; };
+struct FusedF32 { using real = float; static constexpr bool same_orbit = false; };
+struct OrbitF64 { using real = double; static constexpr bool same_orbit = true; };
+
+// One step of one pixel: the derivative at x (times into prod when ACC), then the update.
+//   fused:      t = r*x;  deriv = fma(-2,t,r) = r(1-2x);  x' = fma(-t,x,t) = r x (1-x)            4 instructions
+//   same orbit: deriv = r*|fma(-2,x,1)| (== |r*(1-2x)|, :69);  x' = (r*x)*(1-x) (:76)            6 instructions
+template <typename FL, bool ACC>
+__device__ __forceinline__ void fast_step_one(typename FL::real& x, typename FL::real& prod, typename FL::real r) {
+    using T = typename FL::real;
+    using F = FastTraits<T>;
+    if (FL::same_orbit) {
+        if (ACC) prod = F::mul(prod, F::mul(r, F::abs_(F::fma_((T)-2, x, (T)1))));
+        x = F::mul(F::mul(r, x), F::sub((T)1, x));
+    } else {
+        const T t = F::mul(r, x);
+        if (ACC) prod = F::mul(prod, F::abs_(F::fma_((T)-2, t, r)));
+        x = F::fma_(-t, x, t);
+    }
+}
+
 template <typename T>
 struct FastPixel {
     T x;
@@ -58,9 +84,10 @@ struct FastPixel {
     int valid;
 };
 
-template <typename T, bool ACC>
-__device__ __noinline__ bool fast_careful_chunk(FastPixel<T>* ps, T rA, T rB, T rC, unsigned word, int n,
-                                                unsigned long long* steps) {
+template <typename FL, bool ACC>
+__device__ __noinline__ bool fast_careful_chunk(FastPixel<typename FL::real>* ps, typename FL::real rA, typename FL::real rB,
+                                                typename FL::real rC, unsigned word, int n, unsigned long long* steps) {
+    using T = typename FL::real;
     using F = FastTraits<T>;
     T x = ps->x;
     double extra = ps->extra;
@@ -72,13 +99,13 @@ __device__ __noinline__ bool fast_careful_chunk(FastPixel<T>* ps, T rA, T rB, T 
         const T r = sel == 0 ? rA : (sel == 1 ? rB : rC);
         const T t = F::mul(r, x);
         if (ACC) {
-            const T d = F::abs_(F::fma_((T)-2, t, r));
+            const T d = FL::same_orbit ? F::mul(r, F::abs_(F::fma_((T)-2, x, (T)1))) : F::abs_(F::fma_((T)-2, t, r));
             if (d > (T)0) {
                 extra = __dadd_rn(extra, lyap_log_tab((double)d, g_lyap_logtab, 1));
                 ++valid;
             }
         }
-        x = F::fma_(-t, x, t);
+        x = FL::same_orbit ? F::mul(t, F::sub((T)1, x)) : F::fma_(-t, x, t);
         if (!(x > (T)0 && x < (T)1)) {
             dead = true;
             ++j;
@@ -92,20 +119,17 @@ __device__ __noinline__ bool fast_careful_chunk(FastPixel<T>* ps, T rA, T rB, T 
     return dead;
 }
 
-template <typename T, int P, bool ACC>
-__device__ __forceinline__ void fast_mode_steps(T (&x)[P], T (&prod)[P], const T (&r)[P]) {
-    using F = FastTraits<T>;
+template <typename FL, int P, bool ACC>
+__device__ __forceinline__ void fast_mode_steps(typename FL::real (&x)[P], typename FL::real (&prod)[P],
+                                                const typename FL::real (&r)[P]) {
 #pragma unroll
-    for (int p = 0; p < P; ++p) {
-        const T t = F::mul(r[p], x[p]);
-        if (ACC) prod[p] = F::mul(prod[p], F::abs_(F::fma_((T)-2, t, r[p])));
-        x[p] = F::fma_(-t, x[p], t);
-    }
+    for (int p = 0; p < P; ++p) fast_step_one<FL, ACC>(x[p], prod[p], r[p]);
 }
 
 // fast_careful_chunk for steps [first, first + n) of a region whose selector words start at `sel`.
-template <typename T, bool ACC>
-__device__ __noinline__ bool fast_careful_steps(FastPixel<T>* ps, T rA, T rB, T rC, const unsigned* sel, int wrap, int first, int n,
+template <typename FL, bool ACC>
+__device__ __noinline__ bool fast_careful_steps(FastPixel<typename FL::real>* ps, typename FL::real rA, typename FL::real rB,
+                                                typename FL::real rC, const unsigned* sel, int wrap, int first, int n,
                                                 unsigned long long* steps) {
     bool dead = false;
     int j = first;
@@ -113,7 +137,7 @@ __device__ __noinline__ bool fast_careful_steps(FastPixel<T>* ps, T rA, T rB, T 
     while (j < end && !dead) {
         const int in_word = j & (kStepsPerWord - 1);
         const int m = min(kStepsPerWord - in_word, end - j);
-        dead = fast_careful_chunk<T, ACC>(ps, rA, rB, rC, sel[(j / kStepsPerWord) % wrap] >> (2 * in_word), m, steps);
+        dead = fast_careful_chunk<FL, ACC>(ps, rA, rB, rC, sel[(j / kStepsPerWord) % wrap] >> (2 * in_word), m, steps);
         j += m;
     }
     return dead;
@@ -146,9 +170,11 @@ __host__ __device__ constexpr int strips_in_groups(int ng) {
 // Run-time specialisation (see lyap_jit.cu): NG two-step groups whose patterns are compile-time constants
 // (PATS: 4 bits per group, repeating every KG groups), as one straight-line block; the products are stripped
 // every kRenorm steps and after the last group.
-template <typename T, int P, bool ACC, int KG, unsigned long long PATS, int NG, int GI = 0>
-__device__ __forceinline__ void fast_fixed_groups(T (&x)[P], T (&prod)[P], int (&esum)[P], int (&emin)[P],
-                                                  const T (&rA)[P], const T (&rB)[P], const T (&rC)[P]) {
+template <typename FL, int P, bool ACC, int KG, unsigned long long PATS, int NG, int GI = 0>
+__device__ __forceinline__ void fast_fixed_groups(typename FL::real (&x)[P], typename FL::real (&prod)[P], int (&esum)[P],
+                                                  int (&emin)[P], const typename FL::real (&rA)[P],
+                                                  const typename FL::real (&rB)[P], const typename FL::real (&rC)[P]) {
+    using T = typename FL::real;
     using F = FastTraits<T>;
     if constexpr (GI < NG) {
         constexpr unsigned pat = (unsigned)((PATS >> (4 * (GI % KG))) & 15ull);
@@ -159,13 +185,11 @@ __device__ __forceinline__ void fast_fixed_groups(T (&x)[P], T (&prod)[P], int (
 #pragma unroll
             for (int p = 0; p < P; ++p) {
                 const T r = code == 0 ? rA[p] : (code == 1 ? rB[p] : rC[p]);
-                const T t = F::mul(r, x[p]);
-                if (ACC) prod[p] = F::mul(prod[p], F::abs_(F::fma_((T)-2, t, r)));
-                x[p] = F::fma_(-t, x[p], t);
+                fast_step_one<FL, ACC>(x[p], prod[p], r);
             }
         }
         if (ACC && ((2 * (GI + 1)) % F::kRenorm == 0 || GI == NG - 1)) strip_products<T, P>(prod, esum, emin);
-        fast_fixed_groups<T, P, ACC, KG, PATS, NG, GI + 1>(x, prod, esum, emin, rA, rB, rC);
+        fast_fixed_groups<FL, P, ACC, KG, PATS, NG, GI + 1>(x, prod, esum, emin, rA, rB, rC);
     }
 }
 
@@ -177,9 +201,10 @@ template <>
 __device__ __forceinline__ bool ordinary_param_t<float>(float r) { return r > 0x1p-20f && r < 0x1p5f; }
 
 // Body shared by the precompiled kernel (KG == 0) and a run-time specialised instance (KG > 0).
-template <typename T, int P, int THREADS, int KG, unsigned long long WU_PATS, unsigned long long ACC_PATS>
+template <typename FL, int P, int THREADS, int KG, unsigned long long WU_PATS, unsigned long long ACC_PATS>
 __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __restrict__ out64, float* __restrict__ out32,
                                                  unsigned long long* __restrict__ steps_out) {
+    using T = typename FL::real;
     using F = FastTraits<T>;
     unsigned long long my_steps = 0;
     const long long tile_px = (long long)THREADS * P;
@@ -253,19 +278,19 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                     if (left >= CS) {
 #pragma unroll 1
                         for (int rep = 0; rep < REP; ++rep) {
-                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
-                            else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
+                            if (acc) fast_fixed_groups<FL, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
+                            else fast_fixed_groups<FL, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         }
                         nstrip = REP * strips_in_groups<T>(CB * KG);
                     } else if (left >= CB * BS) {
-                        if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
-                        else fast_fixed_groups<T, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
+                        if (acc) fast_fixed_groups<FL, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
+                        else fast_fixed_groups<FL, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         nstrip = strips_in_groups<T>(CB * KG);
                     } else if (left >= BS) {
 #pragma unroll 1
                         for (int b = 0; b < n / BS; ++b) {
-                            if (acc) fast_fixed_groups<T, P, true, KG, ACC_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
-                            else fast_fixed_groups<T, P, false, KG, WU_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
+                            if (acc) fast_fixed_groups<FL, P, true, KG, ACC_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
+                            else fast_fixed_groups<FL, P, false, KG, WU_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
                         }
                         nstrip = (n / BS) * strips_in_groups<T>(KG);
                     } else {
@@ -273,17 +298,17 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                         for (int j = s; j < nsteps; ++j) {
                             const unsigned code = (sel[(j / kStepsPerWord) % wrap] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
                             if (acc) {
-                                if (code == 0) fast_mode_steps<T, P, true>(x, prod, rA);
-                                else if (code == 1) fast_mode_steps<T, P, true>(x, prod, rB);
-                                else fast_mode_steps<T, P, true>(x, prod, rC);
+                                if (code == 0) fast_mode_steps<FL, P, true>(x, prod, rA);
+                                else if (code == 1) fast_mode_steps<FL, P, true>(x, prod, rB);
+                                else fast_mode_steps<FL, P, true>(x, prod, rC);
                                 if ((j - s + 1) % F::kRenorm == 0 || j == nsteps - 1) {
                                     strip_products<T, P>(prod, esum, emin);
                                     ++nstrip;
                                 }
                             } else {
-                                if (code == 0) fast_mode_steps<T, P, false>(x, prod, rA);
-                                else if (code == 1) fast_mode_steps<T, P, false>(x, prod, rB);
-                                else fast_mode_steps<T, P, false>(x, prod, rC);
+                                if (code == 0) fast_mode_steps<FL, P, false>(x, prod, rA);
+                                else if (code == 1) fast_mode_steps<FL, P, false>(x, prod, rB);
+                                else fast_mode_steps<FL, P, false>(x, prod, rC);
                             }
                         }
                     }
@@ -302,8 +327,8 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             prod[p] = sp[p];
                             FastPixel<T> ps{sx[p], extra[p], valid[p]};
                             const bool dead =
-                                acc ? fast_careful_steps<T, true>(&ps, rA[p], rB[p], rC[p], sel, wrap, s, n, &my_steps)
-                                    : fast_careful_steps<T, false>(&ps, rA[p], rB[p], rC[p], sel, wrap, s, n, &my_steps);
+                                acc ? fast_careful_steps<FL, true>(&ps, rA[p], rB[p], rC[p], sel, wrap, s, n, &my_steps)
+                                    : fast_careful_steps<FL, false>(&ps, rA[p], rB[p], rC[p], sel, wrap, s, n, &my_steps);
                             x[p] = ps.x;
                             extra[p] = ps.extra;
                             valid[p] = ps.valid;
@@ -344,18 +369,18 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                         const int jn = min(F::kRenorm, n - j0);
                         for (int j = 0; j < jn; ++j, w >>= 2) {
                             const unsigned sel = w & 3u;
-                            if (sel == 0) fast_mode_steps<T, P, true>(x, prod, rA);
-                            else if (sel == 1) fast_mode_steps<T, P, true>(x, prod, rB);
-                            else fast_mode_steps<T, P, true>(x, prod, rC);
+                            if (sel == 0) fast_mode_steps<FL, P, true>(x, prod, rA);
+                            else if (sel == 1) fast_mode_steps<FL, P, true>(x, prod, rB);
+                            else fast_mode_steps<FL, P, true>(x, prod, rC);
                         }
                         strip_products<T, P>(prod, esum, emin);
                     }
                 } else {
                     for (int j = 0; j < n; ++j, w >>= 2) {
                         const unsigned sel = w & 3u;
-                        if (sel == 0) fast_mode_steps<T, P, false>(x, prod, rA);
-                        else if (sel == 1) fast_mode_steps<T, P, false>(x, prod, rB);
-                        else fast_mode_steps<T, P, false>(x, prod, rC);
+                        if (sel == 0) fast_mode_steps<FL, P, false>(x, prod, rA);
+                        else if (sel == 1) fast_mode_steps<FL, P, false>(x, prod, rB);
+                        else fast_mode_steps<FL, P, false>(x, prod, rC);
                     }
                 }
 #pragma unroll
@@ -374,8 +399,8 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                         prod[p] = sp[p];
                         FastPixel<T> ps{sx[p], extra[p], valid[p]};
                         const bool dead =
-                            acc ? fast_careful_chunk<T, true>(&ps, rA[p], rB[p], rC[p], word, n, &my_steps)
-                                : fast_careful_chunk<T, false>(&ps, rA[p], rB[p], rC[p], word, n, &my_steps);
+                            acc ? fast_careful_chunk<FL, true>(&ps, rA[p], rB[p], rC[p], word, n, &my_steps)
+                                : fast_careful_chunk<FL, false>(&ps, rA[p], rB[p], rC[p], word, n, &my_steps);
                         x[p] = ps.x;
                         extra[p] = ps.extra;
                         valid[p] = ps.valid;
@@ -444,19 +469,19 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
 
 constexpr int kFastThreads = 256;
 
-template <typename T, int P, int THREADS>
+template <typename FL, int P, int THREADS>
 __global__ void __launch_bounds__(THREADS)
 k_lambda_fast(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,
               unsigned long long* __restrict__ steps_out) {
-    lambda_fast_body<T, P, THREADS, 0, 0ull, 0ull>(a, out64, out32, steps_out);
+    lambda_fast_body<FL, P, THREADS, 0, 0ull, 0ull>(a, out64, out32, steps_out);
 }
 
-#if defined(LYAP_SPEC_FAST_TYPE)
+#if defined(LYAP_SPEC_FAST)
 // The specialised instance; LYAP_SPEC_* are given on the run-time compiler's command line.
 extern "C" __global__ void __launch_bounds__(LYAP_SPEC_THREADS)
 k_lambda_fast_spec(const __grid_constant__ LambdaArgs a, double* __restrict__ out64, float* __restrict__ out32,
                    unsigned long long* __restrict__ steps_out) {
-    lambda_fast_body<LYAP_SPEC_FAST_TYPE, LYAP_SPEC_P, LYAP_SPEC_THREADS, LYAP_SPEC_KG, LYAP_SPEC_WU_PATS, LYAP_SPEC_ACC_PATS>(
+    lambda_fast_body<LYAP_SPEC_FAST, LYAP_SPEC_P, LYAP_SPEC_THREADS, LYAP_SPEC_KG, LYAP_SPEC_WU_PATS, LYAP_SPEC_ACC_PATS>(
         a, out64, out32, steps_out);
 }
 #endif

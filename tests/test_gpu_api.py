@@ -73,7 +73,8 @@ def test_error_statuses(engine):
     assert status(sequence="") == 2 and b"empty" in lib.lyap_last_error()
     assert status(width=0) == 1 and status(height=-3) == 1
     assert status(iterations=-1) == 1 and status(warmup=-1) == 1
-    assert status(mode=7) == 1
+    assert status(mode=7) == 1 and status(mode=3) == 0
+    assert status(mode=1, iterations=2 ** 24) == 3          # the fast modes' 32-bit exponent sums: at most 2^24 steps
     assert status(row_begin=5, row_end=3) == 1 and status(row_begin=0, row_end=9) == 1
     assert status(iterations=20000) == 0                 # a long run of a short sequence wraps round its period
     assert status(iterations=20000, warmup=20000, sequence="".join("AB"[(i * i) % 3 == 0] for i in range(449))) == 3
@@ -122,6 +123,26 @@ def test_fast_modes_within_stated_tolerance(engine):
         bias = abs(np.mean(lam[chaotic]) - np.mean(exact[chaotic]))
         assert bias < mean_bound, (mode, bias)
         assert fast["rgba"].shape == (512, 512, 4) and np.all(fast["rgba"][..., 3] == 255)
+
+
+def test_orbit_mode_differs_from_exact_only_by_the_accumulation(engine):
+    """LYAP_MODE_FAST_FP64_ORBIT runs the reference's own operations for the orbit and each derivative and only
+    accumulates differently (a running product, one log per pixel).  Stated bounds against the exact frame, on config 1
+    and on the page call (mid-run exits): the same sentinel pixels everywhere, the same executed steps, |d lambda| below
+    1e-12, every stable pixel within 1e-6 relative, and at most one RGBA byte in ten thousand off by one level."""
+    page = dict(min_x=0.0, max_x=4.0, min_y=0.0, max_y=4.0, width=800, height=800, sequence="AB", iterations=1000, warmup=100)
+    for kw in (CONFIGS[1], page):
+        exact = engine.render(L.make_params(**kw), want=("lambda", "rgba"))
+        orbit = engine.render(L.make_params(**kw, mode=L.MODE_FAST_FP64_ORBIT), want=("lambda", "rgba"))
+        le, lo = exact["lambda"], orbit["lambda"]
+        assert np.array_equal(le == -5.0, lo == -5.0)
+        assert orbit["stats"].executed_steps == exact["stats"].executed_steps
+        assert np.max(np.abs(le - lo)) < 1e-12
+        stable = (le < 0) & (le > -4)
+        rel = np.abs(lo[stable] - le[stable]) / np.abs(le[stable])
+        assert np.mean(rel > 1e-6) == 0.0, np.mean(rel > 1e-6)
+        diff = exact["rgba"].astype(int) - orbit["rgba"].astype(int)
+        assert np.max(np.abs(diff)) <= 1 and np.mean(diff != 0) < 1e-4, (np.max(np.abs(diff)), np.mean(diff != 0))
 
 
 def test_peak_microbenchmarks_report_plausible_rates(engine):
