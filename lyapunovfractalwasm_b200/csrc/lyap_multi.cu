@@ -552,13 +552,23 @@ int lyap_multi_create(lyap_multi** out, int32_t n_devices, const int32_t* device
     if (!m) return lyap::set_error(LYAP_ERR_NOMEM, "host allocation failed");
     m->slots.resize(n_devices);
     m->want_nccl = use_nccl != 0;
-    for (int i = 0; i < n_devices; ++i) {
-        m->slots[i].device = devices[i];
-        if (int rc = slot_setup(m->slots[i])) {
-            const std::string msg = lyap_last_error();
-            lyap_multi_destroy(m);
-            return lyap::set_error(rc, msg.c_str());
+    {   // contexts, streams, pinned records: one thread per device (done one after the other this takes ~10 ms per device)
+        std::vector<int> rc(n_devices, LYAP_OK);
+        std::vector<std::string> msg(n_devices);
+        std::vector<std::thread> setup;
+        for (int i = 0; i < n_devices; ++i) {
+            m->slots[i].device = devices[i];
+            setup.emplace_back([m, i, &rc, &msg] {
+                rc[i] = slot_setup(m->slots[i]);
+                if (rc[i] != LYAP_OK) msg[i] = lyap_last_error();   // the message is per thread: carry it over
+            });
         }
+        for (auto& t : setup) t.join();
+        for (int i = 0; i < n_devices; ++i)
+            if (rc[i] != LYAP_OK) {
+                lyap_multi_destroy(m);
+                return lyap::set_error(rc[i], msg[i].c_str());
+            }
     }
     nccl_setup(m);   // a failure here is not fatal: the object then works through the host (see lyap_multi_note)
     if (m->slots[0].device >= 0) {
