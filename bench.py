@@ -589,9 +589,9 @@ def main():
             "flops_per_step": {"warmup": FLOPS_WARM, "accumulated": FLOPS_ACC} if mode == L.MODE_EXACT else FAST_FLOPS,
             "ms_per_launch": ms_lambda,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch on the 4096x4096 frame, from the ncu capture summarised
-            # under profiles/ (not re-measured by this run): 1.9 MB read + 76.1 MB written; less than the 134 MB of stores
+            # under profiles/ (not re-measured by this run): 2.7 MB read + 77.1 MB written; less than the 134 MB of stores
             # because the tail is still in L2 at kernel end
-            "traffic": 78.0e6 * rows_all / 4096 if mode == L.MODE_EXACT and not strong else None,
+            "traffic": 79.7e6 * rows_all / 4096 if mode == L.MODE_EXACT and not strong else None,
             "traffic_source": "constant from the committed ncu capture of this kernel on this frame, scaled by rows; not measured live",
             "hbm": {"algorithmic_bytes_per_launch": out_bytes, "store_gbs": out_bytes / (ms_lambda * 1e-3) / 1e9,
                     "peak_gbs": hbm_peak, "peak_source": "MEASURED_PEAKS.json (measured)" if hbm_peak else "absent"},

@@ -214,7 +214,8 @@ typedef struct lyap_multi_stats {
  * device's memory (lyap_multi_gathered), and out_rgba / out_lambda32, if given, are copied from there.  The gather is
  * posted only after every band has finished, and is timed on its own (stats->ms_gather).
  * Failure handling: every step that needs all bands is preceded by a host-side rendezvous with the deadline
- * (timeout_seconds, <= 0: 60 s), so a band that fails or never arrives gives its error / LYAP_ERR_TIMEOUT before
+ * (timeout_seconds; it covers the kernels too; <= 0: 60 s plus the frame's steps / (1e11 per device)), so a band that
+ * fails or never arrives gives its error / LYAP_ERR_TIMEOUT before
  * any collective is enqueued; afterwards completion is polled (stream state, ncclCommGetAsyncError) against the same
  * deadline, and on expiry or an NCCL error the communicators are aborted: LYAP_ERR_TIMEOUT / LYAP_ERR_COMM. */
 int lyap_multi_render(lyap_multi* m, const lyap_params* p, int32_t flags, double* out_lambda, float* out_lambda32,

@@ -623,7 +623,12 @@ int lyap_multi_render(lyap_multi* m, const lyap_params* p, int32_t flags, double
     if (int rc = lyap::validate_whole_frame(p)) return rc;
     const int n = (int)m->slots.size();
     if (n > p->height) return lyap::set_error(LYAP_ERR_INVALID, "more bands than rows");
-    if (timeout_seconds <= 0) timeout_seconds = 60.0;
+    if (timeout_seconds <= 0) {
+        // default: a minute, plus the frame's work at a tenth of one device's real rate spread over the devices (the
+        // deadline covers the kernels too, so it has to grow with the frame)
+        const double steps = (double)p->width * (double)p->height * ((double)p->warmup + (double)p->iterations);
+        timeout_seconds = 60.0 + steps / (1e11 * n);
+    }
     std::lock_guard<std::mutex> call_lock(m->call_mu);
     const auto t0 = Clock::now();
     BandCall c;
