@@ -593,6 +593,10 @@ def main():
             # because the tail is still in L2 at kernel end
             "traffic": 79.7e6 * rows_all / 4096 if mode == L.MODE_EXACT and not strong else None,
             "traffic_source": "constant from the committed ncu capture of this kernel on this frame, scaled by rows; not measured live",
+            "co_bound": {"pipe": "shared-memory data pipe (the logarithm's two 16-byte table look-ups)", "busy": 0.795,
+                         "source": "l1tex__data_pipe_lsu_wavefronts_mem_shared, % of peak, from the committed ncu capture of this "
+                                   "kernel on the 4096x4096 frame (not measured live); the fp64 stream without the look-ups "
+                                   "runs at 0.96 of the issue rate"} if mode == L.MODE_EXACT else None,
             "hbm": {"algorithmic_bytes_per_launch": out_bytes, "store_gbs": out_bytes / (ms_lambda * 1e-3) / 1e9,
                     "peak_gbs": hbm_peak, "peak_source": "MEASURED_PEAKS.json (measured)" if hbm_peak else "absent"},
         }
