@@ -387,6 +387,33 @@ __device__ unsigned palette_rgba(double t, int palette, const lyap_logtab_entry*
 
 constexpr int kColorThreads = 256;
 
+// one pixel: 3x3 mean in the page's summation order, then the palette
+__device__ __forceinline__ unsigned int colorize_one(const double* __restrict__ norm, long long idx, int width, long long rows,
+                                                     int rows_above, int rows_below, int palette, const lyap_logtab_entry* tab) {
+    const long long y = idx / width;
+    const int x = (int)(idx - y * width);
+    double sum = norm[idx];                       // :292
+    int count = 1;
+#pragma unroll
+    for (int dy = -1; dy <= 1; ++dy) {
+        const long long ny = y + dy;
+        const bool row_ok = (ny >= 0 || rows_above) && (ny < rows || rows_below);
+#pragma unroll
+        for (int dx = -1; dx <= 1; ++dx) {
+            if (dx == 0 && dy == 0) continue;
+            const int nx = x + dx;
+            if (row_ok && nx >= 0 && nx < width) {       // :301
+                sum = __dadd_rn(sum, norm[ny * width + nx]);
+                ++count;
+            }
+        }
+    }
+    const double t = __ddiv_rn(sum, (double)count);      // :307
+    return palette_rgba(t, palette, tab);
+}
+
+// Four consecutive pixels per thread, written as one 16-byte store (a warp writes 512 consecutive bytes); the last few
+// pixels of a frame whose size is not a multiple of four, and a misaligned output, take 4-byte stores.
 __global__ void __launch_bounds__(kColorThreads)
 k_colorize(const double* __restrict__ norm, int width, long long rows, int rows_above, int rows_below, int palette,
            unsigned int* __restrict__ rgba) {
@@ -396,28 +423,22 @@ k_colorize(const double* __restrict__ norm, int width, long long rows, int rows_
         __syncthreads();
     }
     const long long n = rows * (long long)width;
+    const long long nquads = (n + 3) / 4;
     const long long nthreads = (long long)gridDim.x * kColorThreads;
-    for (long long idx = (long long)blockIdx.x * kColorThreads + threadIdx.x; idx < n; idx += nthreads) {
-        const long long y = idx / width;
-        const int x = (int)(idx - y * width);
-        double sum = norm[idx];                       // :292
-        int count = 1;
-#pragma unroll
-        for (int dy = -1; dy <= 1; ++dy) {
-            const long long ny = y + dy;
-            const bool row_ok = (ny >= 0 || rows_above) && (ny < rows || rows_below);
-#pragma unroll
-            for (int dx = -1; dx <= 1; ++dx) {
-                if (dx == 0 && dy == 0) continue;
-                const int nx = x + dx;
-                if (row_ok && nx >= 0 && nx < width) {       // :301
-                    sum = __dadd_rn(sum, norm[ny * width + nx]);
-                    ++count;
-                }
-            }
+    const bool aligned = (reinterpret_cast<uintptr_t>(rgba) & 15) == 0;
+    for (long long q = (long long)blockIdx.x * kColorThreads + threadIdx.x; q < nquads; q += nthreads) {
+        const long long idx0 = 4 * q;
+        if (aligned && idx0 + 4 <= n) {
+            uint4 px;
+            px.x = colorize_one(norm, idx0, width, rows, rows_above, rows_below, palette, tab);
+            px.y = colorize_one(norm, idx0 + 1, width, rows, rows_above, rows_below, palette, tab);
+            px.z = colorize_one(norm, idx0 + 2, width, rows, rows_above, rows_below, palette, tab);
+            px.w = colorize_one(norm, idx0 + 3, width, rows, rows_above, rows_below, palette, tab);
+            *reinterpret_cast<uint4*>(rgba + idx0) = px;
+        } else {
+            for (long long idx = idx0; idx < n && idx < idx0 + 4; ++idx)
+                rgba[idx] = colorize_one(norm, idx, width, rows, rows_above, rows_below, palette, tab);
         }
-        const double t = __ddiv_rn(sum, (double)count);      // :307
-        rgba[idx] = palette_rgba(t, palette, tab);
     }
 }
 
@@ -425,7 +446,7 @@ cudaError_t launch_colorize(const double* norm, int width, long long rows, int r
                             int palette, unsigned char* rgba, int sm_count, cudaStream_t st) {
     const long long n = rows * (long long)width;
     if (n <= 0) return cudaSuccess;
-    long long want = (n + kColorThreads - 1) / kColorThreads;
+    long long want = ((n + 3) / 4 + kColorThreads - 1) / kColorThreads;
     const long long cap = (long long)sm_count * 64;
     const int grid = (int)(want < cap ? want : cap);
     k_colorize<<<grid, kColorThreads, 0, st>>>(norm, width, rows, rows_above, rows_below, palette,
