@@ -284,6 +284,13 @@ const char* lyap_last_kernel(void);
  * iterations are accepted while 2 * len / gcd(len, 16) <= 896; longer sequences are limited to 14336 steps. */
 int lyap_selector_code(const lyap_params* params, int region, int64_t step, int* code);
 
+/* No counterpart in the reference (host only, needs no GPU).  The key under which a launch with `params` looks for a
+ * lambda-kernel instance made for its sequence: *groups = number of two-step groups after which the parameter choices
+ * of both regions repeat (0: none up to 16, the generic kernel runs), and the 2-bit codes of one such period of the
+ * warm-up and of the accumulation region (4 bits per group).  The build recipe computes the same key for the instances it
+ * embeds; the CPU tests compare the two. */
+int lyap_group_patterns(const lyap_params* params, int* groups, uint64_t* warmup_patterns, uint64_t* accumulation_patterns);
+
 /* ---- measurement ---- */
 
 /* Issue-rate micro-benchmark of the fp64 pipe on the context's device: independent DFMA chains,

@@ -86,6 +86,7 @@ ABI = {
     "lyap_multi_render_frames": (ctypes.c_int, [_P, ctypes.POINTER(LyapParams), ctypes.c_int32, ctypes.POINTER(_P),
                                                 ctypes.POINTER(_P), ctypes.POINTER(RenderStats)]),
     "lyap_selector_code": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.c_int, ctypes.c_int64, ctypes.POINTER(ctypes.c_int)]),
+    "lyap_group_patterns": (ctypes.c_int, [ctypes.POINTER(LyapParams), ctypes.POINTER(ctypes.c_int), c_u64_p, c_u64_p]),
     "lyap_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "lyap_params_default": (None, [ctypes.POINTER(LyapParams)]),
     "lyap_palette_from_name": (ctypes.c_int, [ctypes.c_char_p]),
@@ -170,6 +171,13 @@ def selector_code(params, region, step):
     code = ctypes.c_int(-1)
     _check(load_library().lyap_selector_code(ctypes.byref(params), region, step, ctypes.byref(code)))
     return code.value
+
+
+def group_patterns(params):
+    """lyap_group_patterns: (groups, warm-up patterns, accumulation patterns) -- the key of a kernel instance for the sequence."""
+    kg, wu, acc = ctypes.c_int(-1), ctypes.c_uint64(0), ctypes.c_uint64(0)
+    _check(load_library().lyap_group_patterns(ctypes.byref(params), ctypes.byref(kg), ctypes.byref(wu), ctypes.byref(acc)))
+    return kg.value, wu.value, acc.value
 
 
 NOALLOC_MAX_VALUES = 1 << 32

@@ -214,6 +214,18 @@ int lyap_selector_code(const lyap_params* p, int region, int64_t step, int* code
     return LYAP_OK;
 }
 
+int lyap_group_patterns(const lyap_params* p, int* groups, uint64_t* warmup_patterns, uint64_t* accumulation_patterns) {
+    if (!groups || !warmup_patterns || !accumulation_patterns) return fail(LYAP_ERR_INVALID, "lyap_group_patterns: null output");
+    lyap::LambdaArgs a;
+    Geometry g;
+    if (int rc = build_args(p, &a, &g)) return rc;
+    unsigned long long wu = 0, acc = 0;
+    *groups = lyap::sequence_group_period(a, &wu, &acc);
+    *warmup_patterns = wu;
+    *accumulation_patterns = acc;
+    return LYAP_OK;
+}
+
 const char* lyap_last_error(void) { return g_last_error.c_str(); }
 
 const char* lyap_status_string(int s) {
