@@ -40,10 +40,11 @@ enum lyap_mode {
     LYAP_MODE_EXACT = 0,       /* fp64, reference operation order, one log per step: bit-exact */
     LYAP_MODE_FAST_FP64 = 1,   /* fp64 FMA orbit, running product of derivatives, one log per pixel */
     LYAP_MODE_FAST_FP32 = 2,   /* fp32 orbit and products, integer exponent sum, one log per pixel */
-    LYAP_MODE_FAST_FP64_ORBIT = 3  /* the reference's own operations for the orbit and each derivative (so x, the exits
-                                      and the sentinels are the exact mode's), but the derivatives multiplied into a
-                                      running product with one log per pixel instead of one log per step: lambda
-                                      differs from the exact mode's only by the rounding of that accumulation */
+    LYAP_MODE_FAST_FP64_ORBIT = 3  /* the reference's own operations for the orbit and for 1 - 2x (so x, the exits and
+                                      the sentinels are the exact mode's), but the factors |1 - 2x| multiplied into a
+                                      running product with one log per pixel, and the factors r added as n_A log r_A +
+                                      n_B log r_B (+ n_C log c): lambda differs from the exact mode's only by the
+                                      rounding of that accumulation (below 1e-12) */
 };
 /* The fast modes accept at most 2^24 steps per pixel (warmup + iterations): LYAP_ERR_TOO_LARGE beyond. */
 

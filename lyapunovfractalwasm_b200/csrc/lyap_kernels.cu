@@ -650,7 +650,7 @@ static cudaError_t launch_lambda_fast_t(const LambdaArgs& a, double* out64, floa
     return cudaGetLastError();
 }
 
-// measured best shapes for the instances made for a sequence: fp64 4 pixels/thread, fp32 2 pixels/thread, 512 threads
+// measured best shapes for the instances made for a sequence: fused fp64 4 pixels/thread, fp32 2, same-orbit fp64 3; 512 threads
 cudaError_t launch_lambda_fast64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                  int sm_count, cudaStream_t st) {
     return launch_lambda_fast_t<FusedF64, 4>(a, out64, out32, steps, sm_count, st, 1, 4, "k_lambda_fast<FusedF64,4,256> (generic)");
@@ -663,7 +663,7 @@ cudaError_t launch_lambda_fast32(const LambdaArgs& a, double* out64, float* out3
 
 cudaError_t launch_lambda_orbit64(const LambdaArgs& a, double* out64, float* out32, unsigned long long* steps,
                                   int sm_count, cudaStream_t st) {
-    return launch_lambda_fast_t<OrbitF64, 4>(a, out64, out32, steps, sm_count, st, 3, 4, "k_lambda_fast<OrbitF64,4,256> (generic)");
+    return launch_lambda_fast_t<OrbitF64, 4>(a, out64, out32, steps, sm_count, st, 3, 3, "k_lambda_fast<OrbitF64,4,256> (generic)");
 }
 
 }  // namespace lyap

@@ -62,13 +62,16 @@ struct OrbitF64 { using real = double; static constexpr bool same_orbit = true; 
 
 // One step of one pixel: the derivative at x (times into prod when ACC), then the update.
 //   fused:      t = r*x;  deriv = fma(-2,t,r) = r(1-2x);  x' = fma(-t,x,t) = r x (1-x)            4 instructions
-//   same orbit: deriv = r*|fma(-2,x,1)| (== |r*(1-2x)|, :69);  x' = (r*x)*(1-x) (:76)            6 instructions
+//   same orbit: |fma(-2,x,1)| into the product (deriv = r*|1-2x|, :69; the r's are added as n*log r at the end);
+//               x' = (r*x)*(1-x) (:76)                                                             5 instructions
 template <typename FL, bool ACC>
 __device__ __forceinline__ void fast_step_one(typename FL::real& x, typename FL::real& prod, typename FL::real r) {
     using T = typename FL::real;
     using F = FastTraits<T>;
     if (FL::same_orbit) {
-        if (ACC) prod = F::mul(prod, F::mul(r, F::abs_(F::fma_((T)-2, x, (T)1))));
+        // |r*(1-2x)| = r*|1-2x| for r > 0: only |1-2x| (exact: 2x and 1-2x round nowhere near 0.5) goes into the product;
+        // the factors r are accounted for per pixel at the end, from how many steps used which parameter
+        if (ACC) prod = F::mul(prod, F::abs_(F::fma_((T)-2, x, (T)1)));
         x = F::mul(F::mul(r, x), F::sub((T)1, x));
     } else {
         const T t = F::mul(r, x);
@@ -200,6 +203,22 @@ __device__ __forceinline__ bool ordinary_param_t<double>(double r) { return r > 
 template <>
 __device__ __forceinline__ bool ordinary_param_t<float>(float r) { return r > 0x1p-20f && r < 0x1p5f; }
 
+// how many of the `steps` 2-bit codes in `pats` (step j at bits 2j, 2j+1) equal `code`
+__host__ __device__ constexpr int count_code(unsigned long long pats, int steps, unsigned code) {
+    int n = 0;
+    for (int j = 0; j < steps; ++j) n += ((pats >> (2 * j)) & 3ull) == code ? 1 : 0;
+    return n;
+}
+
+// the same for the first n (<= 16) steps of a selector word, at run time
+__device__ __forceinline__ void count_word_codes(unsigned word, int n, int& c0, int& c1, int& c2) {
+    const unsigned live = n >= 16 ? 0x55555555u : ((1u << (2 * n)) - 1u) & 0x55555555u;
+    const unsigned lo = word & 0x55555555u, hi = (word >> 1) & 0x55555555u;
+    c0 = __popc(~lo & ~hi & live);
+    c1 = __popc(lo & ~hi & live);
+    c2 = __popc(hi & ~lo & live);
+}
+
 // Body shared by the precompiled kernel (KG == 0) and a run-time specialised instance (KG > 0).
 template <typename FL, int P, int THREADS, int KG, unsigned long long WU_PATS, unsigned long long ACC_PATS>
 __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __restrict__ out64, float* __restrict__ out32,
@@ -214,11 +233,20 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
         T x[P], prod[P], rA[P], rB[P], rC[P];
         double extra[P], lam[P];
         int valid[P], esum[P];   // 32 bits are enough: the host admits at most 2^24 steps per pixel in the fast modes
+        int nuse[P][3];          // same-orbit flavour: accumulated steps of accepted chunks by the parameter they used (A, B, C)
         bool done[P], careful_only[P];
-        // lambda from the three partial sums: esum*ln2 + log(mantissa product) + terms logged one by one
-        auto finish = [&](int e, T m, double ex, int nvalid) -> double {
-            const double lsum = __dadd_rn(__fma_rn((double)e, LYAP_LN2, lyap_log_tab((double)m, g_lyap_logtab, 1)), ex);
-            return nvalid > 0 ? __ddiv_rn(lsum, __dmul_rn((double)nvalid, LYAP_LN2)) : -5.0;
+        // lambda from the partial sums: esum*ln2 + log(mantissa product) + terms logged one by one
+        // (+ n_A log r_A + n_B log r_B + n_C log r_C where the product left the parameters out)
+        auto finish = [&](int p) -> double {
+            double lsum = __dadd_rn(__fma_rn((double)esum[p], LYAP_LN2, lyap_log_tab((double)prod[p], g_lyap_logtab, 1)), extra[p]);
+            if (FL::same_orbit) {
+                double rsum = 0.0;
+                if (nuse[p][0] > 0) rsum = __fma_rn((double)nuse[p][0], lyap_log_tab((double)rA[p], g_lyap_logtab, 1), rsum);
+                if (nuse[p][1] > 0) rsum = __fma_rn((double)nuse[p][1], lyap_log_tab((double)rB[p], g_lyap_logtab, 1), rsum);
+                if (nuse[p][2] > 0) rsum = __fma_rn((double)nuse[p][2], lyap_log_tab((double)rC[p], g_lyap_logtab, 1), rsum);
+                lsum = __dadd_rn(lsum, rsum);
+            }
+            return valid[p] > 0 ? __ddiv_rn(lsum, __dmul_rn((double)valid[p], LYAP_LN2)) : -5.0;
         };
         {
             long long row = idx0 / a.width;
@@ -237,6 +265,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                 extra[p] = 0.0;
                 valid[p] = 0;
                 esum[p] = 0;
+                nuse[p][0] = nuse[p][1] = nuse[p][2] = 0;
                 lam[p] = -5.0;
                 done[p] = !inside || ra <= 0.0 || rb <= 0.0;
                 careful_only[p] = !(ordinary_param_t<T>(rA[p]) && ordinary_param_t<T>(rB[p]) && a.fast_ok_c);
@@ -268,6 +297,8 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                     T sx[P], sp[P];
                     int se[P], emin[P];
                     int nstrip = 0;   // strips made in this chunk (the same for every pixel): their bias leaves the sums below
+                    int cuse[3] = {0, 0, 0};   // accumulated steps of this chunk by parameter (same for every pixel)
+                    constexpr int kPer0 = count_code(ACC_PATS, BS, 0), kPer1 = count_code(ACC_PATS, BS, 1), kPer2 = count_code(ACC_PATS, BS, 2);
 #pragma unroll
                     for (int p = 0; p < P; ++p) {
                         sx[p] = x[p];
@@ -282,10 +313,12 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             else fast_fixed_groups<FL, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         }
                         nstrip = REP * strips_in_groups<T>(CB * KG);
+                        cuse[0] = REP * CB * kPer0, cuse[1] = REP * CB * kPer1, cuse[2] = REP * CB * kPer2;
                     } else if (left >= CB * BS) {
                         if (acc) fast_fixed_groups<FL, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         else fast_fixed_groups<FL, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         nstrip = strips_in_groups<T>(CB * KG);
+                        cuse[0] = CB * kPer0, cuse[1] = CB * kPer1, cuse[2] = CB * kPer2;
                     } else if (left >= BS) {
 #pragma unroll 1
                         for (int b = 0; b < n / BS; ++b) {
@@ -293,11 +326,13 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             else fast_fixed_groups<FL, P, false, KG, WU_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
                         }
                         nstrip = (n / BS) * strips_in_groups<T>(KG);
+                        cuse[0] = (n / BS) * kPer0, cuse[1] = (n / BS) * kPer1, cuse[2] = (n / BS) * kPer2;
                     } else {
 #pragma unroll 1
                         for (int j = s; j < nsteps; ++j) {
                             const unsigned code = (sel[(j / kStepsPerWord) % wrap] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
                             if (acc) {
+                                ++cuse[code < 2 ? code : 2];
                                 if (code == 0) fast_mode_steps<FL, P, true>(x, prod, rA);
                                 else if (code == 1) fast_mode_steps<FL, P, true>(x, prod, rB);
                                 else fast_mode_steps<FL, P, true>(x, prod, rC);
@@ -320,6 +355,11 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             if (acc) {
                                 valid[p] += n;
                                 esum[p] -= F::kBias * nstrip;
+                                if (FL::same_orbit) {
+                                    nuse[p][0] += cuse[0];
+                                    nuse[p][1] += cuse[1];
+                                    nuse[p][2] += cuse[2];
+                                }
                             }
                             my_steps += (unsigned long long)n;
                         } else {
@@ -334,7 +374,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             valid[p] = ps.valid;
                             if (dead) {
                                 done[p] = true;
-                                lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
+                                lam[p] = finish(p);
                                 x[p] = (T)0.25;
                             }
                         }
@@ -356,6 +396,8 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                 T sx[P], sp[P];
                 int se[P], emin[P];
                 int nstrip = 0;
+                int cuse[3] = {0, 0, 0};
+                if (FL::same_orbit && acc) count_word_codes(word, n, cuse[0], cuse[1], cuse[2]);
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     sx[p] = x[p];
@@ -392,6 +434,11 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                         if (acc) {
                             valid[p] += n;
                             esum[p] -= F::kBias * nstrip;
+                            if (FL::same_orbit) {
+                                nuse[p][0] += cuse[0];
+                                nuse[p][1] += cuse[1];
+                                nuse[p][2] += cuse[2];
+                            }
                         }
                         my_steps += (unsigned long long)n;
                     } else {
@@ -407,7 +454,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                         if (dead) {
                             // freeze the result now: the abandoned lane keeps running on garbage
                             done[p] = true;
-                            lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
+                            lam[p] = finish(p);
                             x[p] = (T)0.25;
                         }
                     }
@@ -417,7 +464,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
 
 #pragma unroll
         for (int p = 0; p < P; ++p)
-            if (!done[p]) lam[p] = finish(esum[p], prod[p], extra[p], valid[p]);
+            if (!done[p]) lam[p] = finish(p);
         // stores through the warp's own staging row in shared memory: 16 bytes per lane, consecutive 512-byte runs per
         // instruction, no block-wide barrier (plain stores for a ragged last tile or a misaligned output pointer)
         const long long tile0 = tile * tile_px;
