@@ -239,7 +239,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
         // (+ n_A log r_A + n_B log r_B + n_C log r_C where the product left the parameters out)
         auto finish = [&](int p) -> double {
             double lsum = __dadd_rn(__fma_rn((double)esum[p], LYAP_LN2, lyap_log_tab((double)prod[p], g_lyap_logtab, 1)), extra[p]);
-            if (FL::same_orbit) {
+            if constexpr (FL::same_orbit) {
                 double rsum = 0.0;
                 if (nuse[p][0] > 0) rsum = __fma_rn((double)nuse[p][0], lyap_log_tab((double)rA[p], g_lyap_logtab, 1), rsum);
                 if (nuse[p][1] > 0) rsum = __fma_rn((double)nuse[p][1], lyap_log_tab((double)rB[p], g_lyap_logtab, 1), rsum);
@@ -265,7 +265,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                 extra[p] = 0.0;
                 valid[p] = 0;
                 esum[p] = 0;
-                nuse[p][0] = nuse[p][1] = nuse[p][2] = 0;
+                if constexpr (FL::same_orbit) nuse[p][0] = nuse[p][1] = nuse[p][2] = 0;
                 lam[p] = -5.0;
                 done[p] = !inside || ra <= 0.0 || rb <= 0.0;
                 careful_only[p] = !(ordinary_param_t<T>(rA[p]) && ordinary_param_t<T>(rB[p]) && a.fast_ok_c);
@@ -313,12 +313,12 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             else fast_fixed_groups<FL, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         }
                         nstrip = REP * strips_in_groups<T>(CB * KG);
-                        cuse[0] = REP * CB * kPer0, cuse[1] = REP * CB * kPer1, cuse[2] = REP * CB * kPer2;
+                        if constexpr (FL::same_orbit) cuse[0] = REP * CB * kPer0, cuse[1] = REP * CB * kPer1, cuse[2] = REP * CB * kPer2;
                     } else if (left >= CB * BS) {
                         if (acc) fast_fixed_groups<FL, P, true, KG, ACC_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         else fast_fixed_groups<FL, P, false, KG, WU_PATS, CB * KG>(x, prod, esum, emin, rA, rB, rC);
                         nstrip = strips_in_groups<T>(CB * KG);
-                        cuse[0] = CB * kPer0, cuse[1] = CB * kPer1, cuse[2] = CB * kPer2;
+                        if constexpr (FL::same_orbit) cuse[0] = CB * kPer0, cuse[1] = CB * kPer1, cuse[2] = CB * kPer2;
                     } else if (left >= BS) {
 #pragma unroll 1
                         for (int b = 0; b < n / BS; ++b) {
@@ -326,13 +326,17 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             else fast_fixed_groups<FL, P, false, KG, WU_PATS, KG>(x, prod, esum, emin, rA, rB, rC);
                         }
                         nstrip = (n / BS) * strips_in_groups<T>(KG);
-                        cuse[0] = (n / BS) * kPer0, cuse[1] = (n / BS) * kPer1, cuse[2] = (n / BS) * kPer2;
+                        if constexpr (FL::same_orbit) cuse[0] = (n / BS) * kPer0, cuse[1] = (n / BS) * kPer1, cuse[2] = (n / BS) * kPer2;
                     } else {
 #pragma unroll 1
                         for (int j = s; j < nsteps; ++j) {
                             const unsigned code = (sel[(j / kStepsPerWord) % wrap] >> (2 * (j & (kStepsPerWord - 1)))) & 3u;
                             if (acc) {
-                                ++cuse[code < 2 ? code : 2];
+                                if constexpr (FL::same_orbit) {
+                                    if (code == 0) ++cuse[0];
+                                    else if (code == 1) ++cuse[1];
+                                    else ++cuse[2];
+                                }
                                 if (code == 0) fast_mode_steps<FL, P, true>(x, prod, rA);
                                 else if (code == 1) fast_mode_steps<FL, P, true>(x, prod, rB);
                                 else fast_mode_steps<FL, P, true>(x, prod, rC);
@@ -355,7 +359,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                             if (acc) {
                                 valid[p] += n;
                                 esum[p] -= F::kBias * nstrip;
-                                if (FL::same_orbit) {
+                                if constexpr (FL::same_orbit) {
                                     nuse[p][0] += cuse[0];
                                     nuse[p][1] += cuse[1];
                                     nuse[p][2] += cuse[2];
@@ -397,7 +401,9 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                 int se[P], emin[P];
                 int nstrip = 0;
                 int cuse[3] = {0, 0, 0};
-                if (FL::same_orbit && acc) count_word_codes(word, n, cuse[0], cuse[1], cuse[2]);
+                if constexpr (FL::same_orbit) {
+                    if (acc) count_word_codes(word, n, cuse[0], cuse[1], cuse[2]);
+                }
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     sx[p] = x[p];
@@ -434,7 +440,7 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                         if (acc) {
                             valid[p] += n;
                             esum[p] -= F::kBias * nstrip;
-                            if (FL::same_orbit) {
+                            if constexpr (FL::same_orbit) {
                                 nuse[p][0] += cuse[0];
                                 nuse[p][1] += cuse[1];
                                 nuse[p][2] += cuse[2];
