@@ -27,31 +27,34 @@ static cudaError_t launch_exact_variant(const LambdaArgs& a, double* out64, floa
     // the attribute is per device and cheap to set; doing it on every launch keeps this thread- and device-safe
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    const long long tile_px = (long long)THREADS * P;
+    const long long tile_px = (long long)THREADS * P;     // one round of a block's warps (work is dealt out per warp)
     const long long tiles = (a.n_pixels + tile_px - 1) / tile_px;
     if (tiles <= 0) return cudaSuccess;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     kern<<<grid, THREADS, smem, st>>>(a, out64, out32, steps);
-    static const char* const names[3] = {"k_lambda_exact<2,512> (generic: patterns dispatched every 2 steps)",
-                                         "k_lambda_exact<3,512> (generic: patterns dispatched every 2 steps)",
-                                         "k_lambda_exact<4,512> (generic: patterns dispatched every 2 steps)"};
+    static const char* const names[2] = {"k_lambda_exact<2,512> (generic: patterns dispatched every 2 steps)",
+                                         "k_lambda_exact<3,512> (generic: patterns dispatched every 2 steps)"};
     note_lambda_kernel(names[P - 2]);
     return cudaGetLastError();
 }
 
-// Pixels per thread for a launch of n pixels.  Large frames: 3 (measured best on B200).  Small frames are
-// dominated by how many rounds of tiles the busiest SM runs, so the count that minimises rounds * pixels-per-thread
-// (weighted by each shape's measured per-pixel cost) is taken; `spec` says that the 2- and 3-pixel shapes can run as
-// instances compiled for the sequence, which are faster.
+// Pixels per thread for a launch of n pixels.  Large frames: 3 (measured best on B200).  A frame of only a few rounds of
+// warp-tiles is dominated by its last, partly filled round, in which the few warps still working run faster than in a
+// full round but not in proportion (one warp alone reaches under half of its scheduler's fp64 rate); the shape with the
+// smaller estimate of (full rounds + last round) x per-pixel cost is taken.  `spec`: the shapes run as instances made for
+// the sequence, which are faster.
 static int exact_pixels_per_thread(long long n_pixels, int sm_count, bool spec) {
-    const int cand[3] = {3, 2, 4};
-    const double cost[3] = {spec ? 0.92 : 1.0, spec ? 0.95 : 1.035, 1.015};
+    const int cand[2] = {3, 2};
+    const double cost[2] = {spec ? 0.92 : 1.0, spec ? 0.95 : 1.035};
+    const double warps = (double)sm_count * 16.0;
     int best = 3;
     double best_t = 1e300;
-    for (int i = 0; i < 3; ++i) {
-        const long long tiles = (n_pixels + 512LL * cand[i] - 1) / (512LL * cand[i]);
-        const long long rounds = (tiles + sm_count - 1) / sm_count;
-        const double t = (double)rounds * cand[i] * cost[i];
+    for (int i = 0; i < 2; ++i) {
+        const double tiles = (double)((n_pixels + 32LL * cand[i] - 1) / (32LL * cand[i]));
+        const double rounds = tiles / warps;
+        const double full = (double)(long long)rounds, frac = rounds - full;
+        const double last = frac <= 0.0 ? 0.0 : (frac < 0.45 ? 0.45 : frac);
+        const double t = (full + last) * cand[i] * cost[i];
         if (t < best_t * 0.999) {
             best_t = t;
             best = cand[i];
@@ -83,7 +86,7 @@ cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32
     unsigned long long wu_pats = 0, acc_pats = 0;
     const bool spec = mode != 0 && sequence_group_period(a, &wu_pats, &acc_pats) > 0;
     const int ppt = exact_pixels_per_thread(a.n_pixels, sm_count, spec);
-    if (ppt <= 3) {   // with 4 pixels per thread the specialised instance measured slower
+    {
         bool launched = false;
         const cudaError_t e = launch_lambda_spec(a, out64, out32, steps, sm_count, st, 0, ppt, 512, exact_smem_bytes(512, ppt),
                                                  mode, &launched);
@@ -91,7 +94,6 @@ cudaError_t launch_lambda_exact(const LambdaArgs& a, double* out64, float* out32
         if (launched) return cudaSuccess;
     }
     if (ppt == 2) return LYAP_VARIANT(2, 512, 2);
-    if (ppt == 4) return LYAP_VARIANT(4, 512, 2);
     return LYAP_VARIANT(3, 512, 2);
 #undef LYAP_VARIANT
 }

@@ -235,19 +235,6 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
         int valid[P], esum[P];   // 32 bits are enough: the host admits at most 2^24 steps per pixel in the fast modes
         int nuse[P][3];          // same-orbit flavour: accumulated steps of accepted chunks by the parameter they used (A, B, C)
         bool done[P], careful_only[P];
-        // lambda from the partial sums: esum*ln2 + log(mantissa product) + terms logged one by one
-        // (+ n_A log r_A + n_B log r_B + n_C log r_C where the product left the parameters out)
-        auto finish = [&](int p) -> double {
-            double lsum = __dadd_rn(__fma_rn((double)esum[p], LYAP_LN2, lyap_log_tab((double)prod[p], g_lyap_logtab, 1)), extra[p]);
-            if constexpr (FL::same_orbit) {
-                double rsum = 0.0;
-                if (nuse[p][0] > 0) rsum = __fma_rn((double)nuse[p][0], lyap_log_tab((double)rA[p], g_lyap_logtab, 1), rsum);
-                if (nuse[p][1] > 0) rsum = __fma_rn((double)nuse[p][1], lyap_log_tab((double)rB[p], g_lyap_logtab, 1), rsum);
-                if (nuse[p][2] > 0) rsum = __fma_rn((double)nuse[p][2], lyap_log_tab((double)rC[p], g_lyap_logtab, 1), rsum);
-                lsum = __dadd_rn(lsum, rsum);
-            }
-            return valid[p] > 0 ? __ddiv_rn(lsum, __dmul_rn((double)valid[p], LYAP_LN2)) : -5.0;
-        };
         {
             long long row = idx0 / a.width;
             int col = (int)(idx0 - row * a.width);
@@ -275,6 +262,20 @@ __device__ __forceinline__ void lambda_fast_body(const LambdaArgs& a, double* __
                 }
             }
         }
+
+        // lambda from the partial sums: esum*ln2 + log(mantissa product) + terms logged one by one
+        // (+ n_A log r_A + n_B log r_B + n_C log r_C where the product left the parameters out)
+        auto finish = [&](int p) -> double {
+            double lsum = __dadd_rn(__fma_rn((double)esum[p], LYAP_LN2, lyap_log_tab((double)prod[p], g_lyap_logtab, 1)), extra[p]);
+            if constexpr (FL::same_orbit) {
+                double rsum = 0.0;
+                if (nuse[p][0] > 0) rsum = __fma_rn((double)nuse[p][0], lyap_log_tab((double)rA[p], g_lyap_logtab, 1), rsum);
+                if (nuse[p][1] > 0) rsum = __fma_rn((double)nuse[p][1], lyap_log_tab((double)rB[p], g_lyap_logtab, 1), rsum);
+                if (nuse[p][2] > 0) rsum = __fma_rn((double)nuse[p][2], lyap_log_tab((double)rC[p], g_lyap_logtab, 1), rsum);
+                lsum = __dadd_rn(lsum, rsum);
+            }
+            return valid[p] > 0 ? __ddiv_rn(lsum, __dmul_rn((double)valid[p], LYAP_LN2)) : -5.0;
+        };
 
         for (int region = 0; region < 2; ++region) {
             const bool acc = region == 1;
