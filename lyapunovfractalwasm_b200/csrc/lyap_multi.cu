@@ -288,8 +288,12 @@ void nccl_abort(lyap_multi* m, const char* why) {
 
 // Waits on the host until everything enqueued on the slot's streams is done, polling so that a deadline and an
 // asynchronous NCCL error can end the wait.  Never blocks inside the driver on work that may depend on a peer.
-int wait_streams(lyap_multi* m, Slot& s, Clock::time_point deadline, bool watch_nccl) {
+int wait_streams(lyap_multi* m, Slot& s, Clock::time_point deadline, bool watch_nccl, Rendezvous* rv = nullptr) {
     for (;;) {
+        if (rv) {   // another band has failed: what this one waits for may depend on it, so stop waiting now
+            std::lock_guard<std::mutex> lk(rv->mu);
+            if (rv->failed) return lyap::set_error(rv->status, rv->error.c_str());
+        }
         const cudaError_t a = cudaStreamQuery(s.stream), b = cudaStreamQuery(s.copy);
         if (a != cudaSuccess && a != cudaErrorNotReady)
             return lyap::set_error(LYAP_ERR_CUDA, (std::string("stream: ") + cudaGetErrorString(a)).c_str());
@@ -460,7 +464,7 @@ void band_worker(BandCall& c, int r) {
     if ((gather_rgba || gather_l32) && n > 1) {
         // The gather is posted only once every band is known to be finished and healthy: a send never waits on a device
         // that is still computing (so the gather's time is its own) and never on one that failed.
-        if (int rc = wait_streams(m, s, c.deadline, c.use_nccl)) return bail(rc);
+        if (int rc = wait_streams(m, s, c.deadline, c.use_nccl, &rv)) return bail(rc);
         if (!meet(rv, 1, c.deadline, "gather")) return;
         const size_t band_px = (size_t)rows_own * W;
         nvtxRangePushA("lyap: gather to the first device");
@@ -515,7 +519,7 @@ void band_worker(BandCall& c, int r) {
         if (gather_rgba && c.out_rgba) WCU(cudaMemcpyAsync(c.out_rgba, m->gathered_rgba.p, (size_t)H * W * 4, cudaMemcpyDeviceToHost, st));
         if (gather_l32 && c.out_l32) WCU(cudaMemcpyAsync(c.out_l32, m->gathered_l32.p, (size_t)H * W * 4, cudaMemcpyDeviceToHost, st));
     }
-    if (int rc = wait_streams(m, s, c.deadline, c.use_nccl)) return bail(rc);
+    if (int rc = wait_streams(m, s, c.deadline, c.use_nccl, &rv)) return bail(rc);
     {
         float ms_l = 0, ms_d = 0, ms_g = 0;
         cudaEventElapsedTime(&ms_l, s.ev[0], s.ev[1]);
@@ -650,8 +654,9 @@ int lyap_multi_render(lyap_multi* m, const lyap_params* p, int32_t flags, double
     for (auto& w : workers) w.join();
     if (workers.empty()) return lyap::set_error(LYAP_ERR_TIMEOUT, "lyap_multi_render: no band arrived");
     if (c.rv.status != LYAP_OK) {
-        if (c.use_nccl && (c.rv.status == LYAP_ERR_TIMEOUT || c.rv.status == LYAP_ERR_COMM) && c.rv.arrived[0] == n)
-            nccl_abort(m, "aborted after a failed or overdue collective");   // collectives were posted: do not leave them waiting
+        // once every band had passed the first rendezvous, collectives may have been posted that a failed band will never
+        // join: abort them before waiting for the streams below
+        if (c.use_nccl && c.rv.arrived[0] == n) nccl_abort(m, "aborted after a failed or overdue call");
         for (Slot& s : m->slots) {   // whatever was enqueued must be off the buffers before the next call
             if (s.device < 0) continue;
             cudaSetDevice(s.device);
