@@ -71,10 +71,9 @@ def _worker(rank, world, port, outdir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
 
     def allreduce(lo, hi):
-        t_lo, t_hi = torch.tensor([lo], dtype=torch.float64), torch.tensor([hi], dtype=torch.float64)
-        dist.all_reduce(t_lo, op=dist.ReduceOp.MIN)
-        dist.all_reduce(t_hi, op=dist.ReduceOp.MAX)
-        return float(t_lo), float(t_hi)
+        pair = torch.tensor([lo, -hi], dtype=torch.float64)      # one all-reduce serves both ends: min over (min, -max)
+        dist.all_reduce(pair, op=dist.ReduceOp.MIN)
+        return float(pair[0]), -float(pair[1])
 
     res = bands.render_band(OracleBackend(), KW, rank, world, allreduce, palette=0)
     np.savez(os.path.join(outdir, "rank%d.npz" % rank), lam=res["lambda"], norm=res["norm"], rgba=res["rgba"],
